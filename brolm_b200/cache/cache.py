@@ -10,7 +10,9 @@ Layers whose needs are equal form a *group* with storage of its own:
   index ``p % ring``, so a sequence never holds more than ``ring/page_size``
   pages of it however long it grows;
 * a state group holds one tensor of fixed shape per (layer, slot), zeroed when
-  the slot is taken.
+  the slot is taken;
+* a group without values keeps one row per token that is key and value at once
+  (latent attention), in the keys' store alone.
 
 Storage of a key/value group is ``[layer][page][kv_head][page_size][head_dim]``
 for keys and the same for values; all layers of a group share the page ids, so
@@ -35,10 +37,13 @@ PAGE_SIZE = 64
 
 @dataclasses.dataclass(frozen=True)
 class KVSpec:
-    """Keys and values of ``n_kv`` heads of ``head_dim``; ``window`` None keeps all."""
+    """Keys and values of ``n_kv`` heads of ``head_dim``; ``window`` None keeps all.
+    ``values`` False: one row per token that is key and value at once (a latent that the mixer
+    projects up itself); the group then has one store and ``v`` is ``k``."""
     n_kv: int
     head_dim: int
     window: Optional[int] = None
+    values: bool = True
 
 
 @dataclasses.dataclass(frozen=True)
@@ -64,7 +69,7 @@ class KVGroup:
         self.pool = PagePool(num_pages)
         shape = (len(entries), num_pages, spec.n_kv, page_size, spec.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if spec.values else self.k
         self.pages: dict[int, list[int]] = {}     # slot -> page ids in ring/position order
 
     @property
@@ -116,7 +121,8 @@ class Cache:
     """
 
     def __init__(self, specs: Sequence[Optional[CacheSpec]], max_tokens: int, dtype: torch.dtype,
-                 device: Union[str, torch.device], page_size: int = PAGE_SIZE, max_slots: Optional[int] = None):
+                 device: Union[str, torch.device], page_size: int = PAGE_SIZE, max_slots: Optional[int] = None,
+                 keep_last_token: bool = False):
         if max_tokens <= 0:
             raise CacheError("max_tokens must be positive")
         if page_size <= 0 or page_size % 32 != 0:
@@ -135,6 +141,10 @@ class Cache:
         self.kv_groups: list[KVGroup] = []
         self.state_groups: list[StateGroup] = []
         self.entries: list[Optional[CacheEntry]] = [None] * len(specs)
+        # the last token every slot was given (an embedding that looks at pairs of tokens reads and writes it
+        # on the device); the spare row is the padding rows'
+        self.last_token = torch.zeros(self.max_slots + 1, dtype=torch.int32, device=self.device) \
+            if keep_last_token else None
 
         by_spec: dict[CacheSpec, list[int]] = {}
         for i, s in enumerate(specs):
@@ -282,7 +292,7 @@ class Cache:
     def bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += g.k.numel() * g.k.element_size() * 2
+            n += g.k.numel() * g.k.element_size() * (2 if g.spec.values else 1)
         for g in self.state_groups:
             n += g.data.numel() * g.data.element_size()
         return n

@@ -128,7 +128,9 @@ def registered_architectures() -> list[str]:
 
 def architecture_of(raw: dict[str, Any]) -> Architecture:
     """Pick the architecture a parsed config.json names."""
-    names = raw.get("architectures") or []
+    names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):       # some families write one name instead of a list
+        names.append(raw["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]

@@ -107,6 +107,8 @@ struct MmaArgs {
     float* part_o;          // [B][n_q][n_splits][hd]
     float* part_ml;         // [B][n_q][n_splits][2]  (max in log2 units, sum)
     int merge_here;         // decoding: the last block of a (sequence, kv head) merges the splits itself
+    const float* sink;      // [n_q] or null: exp(sink[head]) joins the softmax's denominator, with no value
+    int shared_kv;          // decoding: the values are the keys' rows themselves (one tile serves both)
 };
 
 // Tickets of the split-KV decode kernel, one per (sequence, kv head); zero between launches.
@@ -307,8 +309,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         const int r = warp * 16 + (lane >> 2) + 8 * i;
         if (r >= rows_here) continue;
-        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
         const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
+        if (a.sink && m[i] > -INFINITY) sum += fast_exp2(a.sink[head] * LOG2E - m[i]);
+        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
         bf16* dst = a.out + (size_t)(q0 + tok) * a.out_stride + head * hd + (lane & 3) * 2;
 #pragma unroll
         for (int d = 0; d < HD_MAX / 8; ++d) {
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
             const int kp = t * KT + r;
             const int bytes = (kp >= key_lo && kp <= pos) ? 16 : 0;   // places never written read as zero
             cp_async16(kb + off, a.k_pages + src + r * hd + c * 8, bytes);
-            cp_async16(vb + off, a.v_pages + src + r * hd + c * 8, bytes);
+            if (!a.shared_kv) cp_async16(vb + off, a.v_pages + src + r * hd + c * 8, bytes);
         }
     };
 #pragma unroll
@@ -397,7 +400,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     const uint32_t jq = lane >> 4, jk = (lane >> 3) & 1, jv = lane >> 4;
     const uint32_t q_addr = qs_base + (lane & 15) * rowb + ((swz ? (jq ^ (x & 1u)) : jq) << 4);
     const uint32_t k_thr = (warp * 16 + (lane & 7) + ((lane >> 4) << 3)) * rowb + ((swz ? (jk ^ (x & 1u)) : jk) << 4);
-    const uint32_t v_thr = KT * rowb + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * rowb +
+    const uint32_t v_thr = (a.shared_kv ? 0u : KT * rowb) + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * rowb +
                            ((swz ? (jv ^ (x & 1u)) : jv) << 4);
 
     float o[HD_MAX / 8][4];
@@ -524,6 +527,14 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
             }
         }
         const int head = g * a.group + row;
+        if (a.sink && split == 0) {
+            // the sink joins the first split's statistics: a key of score sink[head] with a zero value
+            const float sk = a.sink[head] * LOG2E, m2 = fmaxf(mx, sk);
+            const float f = mx > -INFINITY ? fast_exp2(mx - m2) : 0.0f;
+            sum = sum * f + fast_exp2(sk - m2);
+            acc *= f;
+            mx = m2;
+        }
         if (a.n_splits == 1) {
             a.out[(size_t)q_row * a.out_stride + head * hd + d] = __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
         } else {

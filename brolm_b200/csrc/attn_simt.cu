@@ -19,6 +19,8 @@
 // Scores follow wlejon/brolm src/gemma2.cpp:360-367: s = (q.k) * scale, then
 // cap * tanh(s / cap), then the mask, then softmax.  Key j is visible from a
 // query at position p iff 0 <= p - j < window (window <= 0: no window).
+// With a sink, a learned number per query head, the softmax's denominator also
+// holds exp(sink): a key that is always visible, is not scaled and has no value.
 #include "common.cuh"
 
 namespace {
@@ -46,6 +48,7 @@ struct AttnArgs {
     int n_kv, group, hd;
     float scale, cap;
     int window;
+    const float* sink;        // [n_kv * group] or null: exp(sink[head]) joins the softmax's denominator, with no value
 };
 
 // DPL: output dims per lane = ceil(hd / 32) rounded up to the instantiated size.
@@ -186,7 +189,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
         const int r = warp * RPW + i;
         if (r >= rows_here) continue;
         const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
-        const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;
+        float den = l[i];
+        if (a.sink && m[i] > -INFINITY) den += expf(a.sink[head] - m[i]);
+        const float inv = den > 0.0f ? 1.0f / den : 0.0f;
         T* dst = og + (size_t)(q0 + tok) * a.out_stride + head * hd;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) {
@@ -236,8 +241,8 @@ int dispatch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream
 BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out, int out_stride, const void* cu_q,
                               const void* kv_len, const void* k, const void* v, int kv_stride, const void* k_pages,
                               const void* v_pages, const void* page_table, int pt_stride, int ring, int page_size,
-                              int n_kv, int group, int hd, float scale, float cap, int window, int batch,
-                              int max_q_len, cudaStream_t stream) {
+                              int n_kv, int group, int hd, float scale, float cap, int window, const void* sink,
+                              int batch, int max_q_len, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     if (hd <= 0 || hd % 8 != 0 || hd > 512 || group <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
     if (q_stride % 8 != 0 || out_stride % 8 != 0) return BROLM_ERR_ALIGNMENT;
@@ -254,7 +259,7 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
     a.k = k; a.v = v; a.kv_stride = kv_stride;
     a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = (const int32_t*)page_table;
     a.pt_stride = pt_stride; a.ring = ring; a.page_size = page_size;
-    a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window;
+    a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.sink = (const float*)sink;
     if (dtype == BROLM_F32) return dispatch<float>(a, paged, batch, max_q_len, stream);
     if (dtype == BROLM_BF16) return dispatch<bf16>(a, paged, batch, max_q_len, stream);
     return BROLM_ERR_BAD_DTYPE;

@@ -34,6 +34,92 @@ BROLM_API int brolm_embed_scale(const void* ids, const void* table, int table_dt
 }
 
 // ---------------------------------------------------------------------------
+// Embedding plus a hashed table of token pairs:
+//     h[t, :] = table[ids[t]] * scale + pairs[(prev * mul_prev + ids[t] * mul_cur) mod buckets]
+// prev is the token before ids[t] in its sequence: the one before it in this
+// step, or, for the first token a step brings to a sequence that already holds
+// tokens, what `last_token[slot]` kept from the step before.  A sequence's
+// first token (position 0) takes row number `buckets`, the table's last.  The
+// last token a step brings to a sequence is left in `last_token[slot]`.
+// Padding rows (position < 0) take the token row alone and leave nothing.
+// ---------------------------------------------------------------------------
+template <typename W>
+__global__ void embed_pairs_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
+                                   const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ cu_q,
+                                   const int32_t* __restrict__ slots, int32_t* __restrict__ last_token,
+                                   const W* __restrict__ table, const W* __restrict__ pairs, float scale,
+                                   long long mul_prev, long long mul_cur, int buckets, float* __restrict__ out,
+                                   int hidden) {
+    const int t = blockIdx.x;
+    const int id = ids[t], pos = positions[t];
+    const W* row = table + (size_t)id * hidden;
+    float* dst = out + (size_t)t * hidden;
+    if (pos < 0) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]) * scale;
+        return;
+    }
+    const int seq = tok_seq[t], slot = slots[seq];
+    int bucket = buckets;
+    if (pos > 0) {
+        const long long prev = t > cu_q[seq] ? ids[t - 1] : last_token[slot];
+        bucket = (int)((prev * mul_prev + (long long)id * mul_cur) % buckets);
+    }
+    const W* extra = pairs + (size_t)bucket * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(row[i]) * scale + to_float(extra[i]);
+    // every thread of the block has read last_token[slot] before this store: one block per token, and
+    // only the block of a sequence's last token of the step writes its slot
+    __syncthreads();
+    if (threadIdx.x == 0 && t == cu_q[seq + 1] - 1) last_token[slot] = id;
+}
+
+BROLM_API int brolm_embed_pairs(const void* ids, const void* positions, const void* tok_seq, const void* cu_q,
+                                const void* slots, void* last_token, const void* table, const void* pairs,
+                                int table_dtype, float scale, long long mul_prev, long long mul_cur, int buckets,
+                                void* out, int tokens, int hidden, cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (buckets <= 0 || mul_prev < 0 || mul_cur < 0) return BROLM_ERR_BAD_SIZE;
+    if (table_dtype == BROLM_F32)
+        embed_pairs_kernel<float><<<tokens, 256, 0, stream>>>(
+            (const int32_t*)ids, (const int32_t*)positions, (const int32_t*)tok_seq, (const int32_t*)cu_q,
+            (const int32_t*)slots, (int32_t*)last_token, (const float*)table, (const float*)pairs, scale, mul_prev,
+            mul_cur, buckets, (float*)out, hidden);
+    else if (table_dtype == BROLM_BF16)
+        embed_pairs_kernel<bf16><<<tokens, 256, 0, stream>>>(
+            (const int32_t*)ids, (const int32_t*)positions, (const int32_t*)tok_seq, (const int32_t*)cu_q,
+            (const int32_t*)slots, (int32_t*)last_token, (const bf16*)table, (const bf16*)pairs, scale, mul_prev,
+            mul_cur, buckets, (float*)out, hidden);
+    else
+        return BROLM_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Two float streams side by side in the step's element type:
+//     out[t, :] = [a[t, :] | b[t, :]]      (the input of a product over both)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
+                                   int hidden) {
+    const size_t t = blockIdx.x;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        out[t * 2 * hidden + i] = from_float<T>(a[t * hidden + i]);
+        out[t * 2 * hidden + hidden + i] = from_float<T>(b[t * hidden + i]);
+    }
+}
+
+BROLM_API int brolm_concat_cast(const void* a, const void* b, void* out, int out_dtype, int tokens, int hidden,
+                                cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (out_dtype == BROLM_F32)
+        concat_cast_kernel<float><<<tokens, 256, 0, stream>>>((const float*)a, (const float*)b, (float*)out, hidden);
+    else if (out_dtype == BROLM_BF16)
+        concat_cast_kernel<bf16><<<tokens, 256, 0, stream>>>((const float*)a, (const float*)b, (bf16*)out, hidden);
+    else
+        return BROLM_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
 // RMSNorm:  y = x * rsqrt(mean(x^2) + eps) * (offset + w)
 // (src/gemma2.cpp:349; the reference folds the +1 into w at load, :154-175).
 // `rows` (optional) picks the input rows, so that only wanted rows of the

@@ -48,7 +48,9 @@ class DecoderModel:
             built = {name: self._build(spec) for name, spec in bs.part_specs().items()}
             self.blocks.append(part_class("block", bs.kind)(**built))
         self.final_norm = self._build(self.layout.final_norm)
+        self.stream_parts = {name: self._build(spec) for name, spec in self.layout.stream_parts.items()}
         self.embedding: Optional[torch.Tensor] = None
+        self.pair_table: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.loaded = False
         self.generation = 0          # goes up whenever the tensors a captured step points at are replaced
@@ -77,6 +79,8 @@ class DecoderModel:
         out: dict[str, Expected] = {}
         emb = self.layout.embedding
         out[emb.tensor] = Expected((emb.vocab, emb.hidden), "table")
+        if emb.pairs is not None:
+            out[emb.pairs.tensor] = Expected((emb.pairs.buckets + 1, emb.hidden), "table")
         for part, names in self._tensor_names:
             specs = part.param_specs()
             for local, spec in specs.items():
@@ -114,6 +118,10 @@ class DecoderModel:
     def _bind(self, tensors: dict[str, torch.Tensor]) -> None:
         emb, head = self.layout.embedding, self.layout.head
         self.embedding = tensors[emb.tensor]
+        if emb.pairs is not None:
+            self.pair_table = tensors[emb.pairs.tensor]
+            if self.pair_table.dtype != self.embedding.dtype:
+                self.pair_table = self.pair_table.to(self.embedding.dtype)
         if head.tensor in tensors:
             self.head = tensors[head.tensor]
         elif head.tied_to is not None:
@@ -134,7 +142,8 @@ class DecoderModel:
         return specs
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None, max_seq_len: Optional[int] = None) -> Cache:
-        cache = Cache(self.cache_specs(), max_tokens, self.dtype, self.device, max_slots=max_slots)
+        cache = Cache(self.cache_specs(), max_tokens, self.dtype, self.device, max_slots=max_slots,
+                      keep_last_token=self.layout.embedding.pairs is not None)
         positions = min(max_seq_len or cache.max_tokens, cache.max_tokens)
         for part, _ in self._tensor_names:
             part.prepare(positions, self.device)
@@ -148,15 +157,29 @@ class DecoderModel:
             raise RuntimeError("forward: weights not loaded")
         lay = self.layout
         h = torch.empty((ctx.n_tokens, lay.embedding.hidden), dtype=torch.float32, device=self.device)
-        kernels.embed_scale(tokens, self.embedding, lay.embedding.scale, h)
+        emb = lay.embedding
+        if emb.pairs is not None:
+            kernels.embed_pairs(tokens, ctx.positions, ctx.tok_seq, ctx.cu_q, ctx.slots_dev, ctx.cache.last_token,
+                                self.embedding, self.pair_table, emb.scale, emb.pairs.mul_prev, emb.pairs.mul_cur,
+                                emb.pairs.buckets, h)
+        else:
+            kernels.embed_scale(tokens, self.embedding, emb.scale, h)
         sched = lay.schedule
+        # the embedding's output, for the stream parts that look at it again
+        h0 = h.clone() if any(call.before is not None for call in sched) else None
         first = self.blocks[sched[0].block].entry_norm
-        x = first.apply(h, ctx.dtype) if first is not None else None
+        x = first.apply(h, ctx.dtype) if (first is not None and sched[0].before is None) else None
         for i, call in enumerate(sched):
             blk = self.blocks[call.block]
+            if call.before is not None:
+                # the stream is remade here, so the block before could not hand over its norm
+                h = self.stream_parts[call.before].forward(h, h0, ctx)
+                x = blk.entry_norm.apply(h, ctx.dtype) if blk.entry_norm is not None else None
             src = i if call.cache_of is None else call.cache_of
             entry = ctx.cache.entries[src]
-            nxt = self.blocks[sched[i + 1].block].entry_norm if i + 1 < len(sched) else None
+            nxt = None
+            if i + 1 < len(sched) and sched[i + 1].before is None:
+                nxt = self.blocks[sched[i + 1].block].entry_norm
             x = blk.forward(h, x, ctx, entry, call.cache_of is None, nxt)
         head_in = torch.float32 if self.head.dtype == torch.float32 else self.dtype
         if rows.numel() == 0:

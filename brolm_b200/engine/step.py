@@ -191,6 +191,7 @@ class Engine:
         self.device = model.device
         self.vocab = model.layout.embedding.vocab
         parts = [p for blk in model.blocks for p in blk.parts().values() if p is not None] + [model.final_norm]
+        parts += list(model.stream_parts.values())
         self.use_graphs = bool(use_graphs and self.device.type == "cuda" and all(p.graph_safe for p in parts))
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self._graphs_generation = model.generation

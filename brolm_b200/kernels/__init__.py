@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from ctypes import c_float, c_int, c_long, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
 import torch
@@ -222,6 +222,138 @@ def softcap(x: torch.Tensor, out: torch.Tensor, cap: float) -> None:
     assert x.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32 and x.numel() == out.numel()
     f = _fn("core", "brolm_softcap", [c_void_p, c_int, c_void_p, c_longlong, c_float, c_void_p])
     _check(f(_ptr(x), _code(x), _ptr(out), x.numel(), cap, _stream()), "softcap")
+
+
+def embed_pairs(ids: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, cu_q: torch.Tensor,
+                slots: torch.Tensor, last_token: torch.Tensor, table: torch.Tensor, pairs: torch.Tensor, scale: float,
+                mul_prev: int, mul_cur: int, buckets: int, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] * scale + pairs[(prev * mul_prev + ids[t] * mul_cur) % buckets], prev being the
+    token before ids[t] in its sequence (this step's, or ``last_token[slot]`` from the step before); a
+    sequence's first token takes row ``buckets``.  Leaves each sequence's last token in ``last_token``."""
+    for t in (ids, positions, tok_seq, cu_q, slots, last_token):
+        assert t.dtype == torch.int32 and t.is_contiguous()
+    assert out.dtype == torch.float32 and table.is_contiguous() and pairs.is_contiguous() and out.is_contiguous()
+    assert table.dtype == pairs.dtype and pairs.shape == (buckets + 1, table.shape[1])
+    assert positions.numel() == ids.numel() and tok_seq.numel() == ids.numel()
+    f = _fn("core", "brolm_embed_pairs", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_float, c_longlong, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(positions), _ptr(tok_seq), _ptr(cu_q), _ptr(slots), _ptr(last_token), _ptr(table),
+             _ptr(pairs), _code(table), scale, mul_prev, mul_cur, buckets, _ptr(out), ids.numel(), table.shape[1],
+             _stream()), "embed_pairs")
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [a[t] | b[t]] in out's element type; a and b float32 (tokens, hidden)."""
+    assert a.dtype == torch.float32 and b.dtype == torch.float32 and a.shape == b.shape
+    assert a.is_contiguous() and b.is_contiguous() and out.is_contiguous() and out.shape == (a.shape[0], 2 * a.shape[1])
+    f = _fn("core", "brolm_concat_cast", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(a), _ptr(b), _ptr(out), _code(out), a.shape[0], a.shape[1], _stream()), "concat_cast")
+
+
+def latent_rows(proj: torch.Tensor, q_cols: int, positions: torch.Tensor, cos_sin: Optional[torch.Tensor], rotary_dim: int,
+                gain: torch.Tensor, eps: float, heads: int, dn: int, dr: int, rank: int, lat: torch.Tensor,
+                qlat: torch.Tensor, pages: Optional[torch.Tensor] = None,
+                cache_rows: Optional[torch.Tensor] = None) -> None:
+    """The row-wise step of latent attention.  ``proj`` (tokens, q_cols + rank + dr): per head [dn | dr] queries,
+    then the compressed row [rank | dr].  Writes ``lat`` (tokens, Dp) = [rmsnorm(compressed) * gain | rotated key
+    part | zeros], the same row into ``pages`` at ``cache_rows`` (negative: not kept), and the rotated query
+    parts into columns rank .. of every head of ``qlat`` (tokens, heads * Dp)."""
+    Dp = lat.shape[1]
+    assert proj.stride(1) == 1 and proj.shape[1] == q_cols + rank + dr and q_cols == heads * (dn + dr)
+    assert lat.dtype == proj.dtype and qlat.dtype == proj.dtype and gain.dtype == proj.dtype
+    assert lat.is_contiguous() and qlat.is_contiguous() and qlat.shape == (proj.shape[0], heads * Dp)
+    assert gain.is_contiguous() and gain.numel() == rank
+    assert positions.dtype == torch.int32 and positions.numel() == proj.shape[0]
+    if cos_sin is not None:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1:] == (rotary_dim // 2, 2)
+    if pages is not None:
+        assert pages.dtype == proj.dtype and pages.is_contiguous() and pages.shape[-1] == Dp
+        assert cache_rows is not None and cache_rows.dtype == torch.int32 and cache_rows.numel() == proj.shape[0]
+    f = _fn("latent", "brolm_latent_rows", [c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float,
+                                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_int, c_void_p])
+    _check(f(_code(proj), _ptr(proj), proj.stride(0), q_cols, _ptr(positions), _ptr(cos_sin),
+             rotary_dim if cos_sin is not None else 0, _ptr(gain), eps, heads, dn, dr, rank, Dp, _ptr(lat), _ptr(qlat),
+             _ptr(pages), _ptr(cache_rows) if pages is not None else None, proj.shape[0], _stream()), "latent_rows")
+
+
+def route_topk(x: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """ids, weights [tokens, top]: the ``top`` experts with the largest router.x (float32 sums; ties: the lower
+    index), best first, and the logistic function of their scores."""
+    assert x.dtype == router.dtype and x.stride(1) == 1 and router.is_contiguous() and router.shape[1] == x.shape[1]
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
+    assert ids.shape == (x.shape[0], top) and weights.shape == ids.shape
+    f = _fn("grouped", "brolm_route_topk", [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                            c_void_p, c_void_p])
+    _check(f(_code(x), _ptr(x), x.stride(0), _ptr(router), x.shape[0], router.shape[0], x.shape[1], top, _ptr(ids),
+             _ptr(weights), _stream()), "route_topk")
+
+
+GROUP_ROWS = 64          # rows of a tile of the grouped product
+
+
+def group_tiles(pairs: int, experts: int) -> int:
+    """Room the tile list of ``group_pairs`` needs: every expert may end with a tile that is not full."""
+    return (pairs + GROUP_ROWS - 1) // GROUP_ROWS + experts
+
+
+def group_pairs(ids: torch.Tensor, experts: int, perm: torch.Tensor, offsets: torch.Tensor, tiles: torch.Tensor) -> None:
+    """Sort the (token, choice) pairs of ``ids`` [tokens, top] by expert, on the device: ``perm`` [pairs] the
+    pairs in expert order, ``offsets`` [experts + 1] each expert's first row, ``tiles`` [2, group_tiles]
+    (expert, first row) of every 64-row tile, expert -1 beyond the last."""
+    pairs = ids.numel()
+    for t in (ids, perm, offsets, tiles):
+        assert t.dtype == torch.int32 and t.is_contiguous()
+    assert perm.numel() == pairs and offsets.numel() == experts + 1 and tiles.shape == (2, group_tiles(pairs, experts))
+    f = _fn("grouped", "brolm_group_pairs", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                             c_void_p])
+    _check(f(_ptr(ids), pairs, experts, _ptr(perm), _ptr(offsets), _ptr(tiles[0]), _ptr(tiles[1]), tiles.shape[1],
+             _stream()), "group_pairs")
+
+
+def heads_linear(a: torch.Tensor, a_head: int, weight: torch.Tensor, out: torch.Tensor, o_head: int) -> None:
+    """A product per head: out[t, h * o_head + n] = sum_k weight[h, n, k] * a[t, h * a_head + k].
+    ``weight`` [heads, N, K]; a and out are packed rows whose heads lie ``a_head`` / ``o_head`` apart (a head's
+    slice may be wider than K or N).  float32 everywhere, or bfloat16 operands with a bfloat16 or float32 result."""
+    H, N, K = weight.shape
+    assert a.dtype == weight.dtype and weight.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1
+    assert a.shape[0] == out.shape[0] and K <= a_head and N <= o_head
+    assert (H - 1) * a_head + K <= a.shape[1] and (H - 1) * o_head + N <= out.shape[1]
+    assert out.dtype in (torch.float32, a.dtype)
+    f = _fn("grouped", "brolm_heads_linear", [c_int, c_void_p, c_long, c_long, c_void_p, c_long, c_long, c_void_p, c_long,
+                                              c_long, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_code(a), _ptr(a), a.stride(0), a_head, _ptr(weight), K, N * K, _ptr(out), out.stride(0), o_head,
+             1 if out.dtype == torch.float32 else 0, a.shape[0], H, N, K, _stream()), "heads_linear")
+
+
+EXPERT_ACTS = {"none": 0, "relu2": 1}
+
+
+def experts_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, perm: torch.Tensor, offsets: torch.Tensor,
+                   tiles: torch.Tensor, top: int, tokens: int, scale: Optional[torch.Tensor] = None,
+                   activation: str = "none", down: bool = False) -> None:
+    """One of the two products of routed experts over the pairs that ``group_pairs`` sorted.  ``weight``
+    [experts, N, K].  First product (``down`` False): a (tokens, K) the tokens' rows, each pair's row multiplied
+    by ``scale[pair]`` and rounded to the operands' type; out (pairs, N) in expert order, with the activation.
+    Second (``down`` True): a (pairs, K) in expert order; out float32 [top, tokens, N], a pair's result at
+    [its choice, its token]."""
+    E, N, K = weight.shape
+    pairs = perm.numel()
+    assert a.dtype == weight.dtype and weight.is_contiguous() and a.stride(1) == 1 and out.is_contiguous()
+    assert a.shape[1] == K and pairs == top * tokens
+    if down:
+        assert out.dtype == torch.float32 and tuple(out.shape) == (top, tokens, N) and a.shape[0] == pairs
+    else:
+        assert scale is not None and scale.dtype == torch.float32 and scale.numel() == pairs and scale.is_contiguous()
+        assert tuple(out.shape) == (pairs, N) and a.shape[0] == tokens and out.dtype in (torch.float32, a.dtype)
+    if activation not in EXPERT_ACTS:
+        raise KernelError(f"experts_linear: unknown activation '{activation}' (known: {sorted(EXPERT_ACTS)})")
+    f = _fn("grouped", "brolm_experts_linear", [c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_long, c_void_p, c_long,
+                                                c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_code(a), 1 if down else 0, _ptr(a), a.stride(0), _ptr(weight), K, N * K, _ptr(out), N,
+             1 if out.dtype == torch.float32 else 0, EXPERT_ACTS[activation], N, K, _ptr(tiles[0]), _ptr(tiles[1]),
+             _ptr(offsets), _ptr(perm), _ptr(scale), top, tokens, tiles.shape[1], _stream()), "experts_linear")
 
 
 def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -549,8 +681,11 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
                    group: int, head_dim: int, scale: float, cap: float, window: int, batch: int, max_q_len: int,
                    k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
                    k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
-                   page_table: Optional[torch.Tensor] = None, ring: int = 0, page_size: int = 0) -> None:
-    """Exact attention on CUDA cores.  Keys come from (k, v) packed like q, or from cache pages."""
+                   page_table: Optional[torch.Tensor] = None, ring: int = 0, page_size: int = 0,
+                   sink: Optional[torch.Tensor] = None) -> None:
+    """Exact attention on CUDA cores.  Keys come from (k, v) packed like q, or from cache pages.
+    ``sink``: float32 [query heads]; exp(sink) joins every softmax's denominator (a key with no value)."""
+    _check_sink(sink, n_kv * group)
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and q.dtype == out.dtype
     assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
     kv_stride = pt_stride = 0
@@ -565,24 +700,31 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
         kv_stride = k.stride(0)
     f = _fn("attn_simt", "brolm_attn_simt", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                             c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_void_p])
+                                             c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int,
+                                             c_void_p])
     _check(f(_code(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k), _ptr(v),
              kv_stride, _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, ring, page_size, n_kv, group,
-             head_dim, scale, cap, window, batch, max_q_len, _stream()), "attention_simt")
+             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, _stream()), "attention_simt")
+
+
+def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == n_q
 
 
 def attention_prefill_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                           n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int, batch: int,
-                          max_q_len: int) -> None:
+                          max_q_len: int, sink: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention of whole prompts that start at position 0 (bfloat16, head_dim <= 256)."""
+    _check_sink(sink, n_kv * group)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert k.stride(0) == v.stride(0) and cu_q.dtype == torch.int32
     f = _fn("attn_mma", "brolm_attn_prefill_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                                   c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int,
-                                                   c_void_p])
+                                                   c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int,
+                                                   c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(k), _ptr(v), k.stride(0), n_kv, group,
-             head_dim, scale, cap, window, batch, max_q_len, _stream()), "attention_prefill_mma")
+             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, _stream()), "attention_prefill_mma")
 
 
 def attention_prefill_tc_ok(head_dim: int, group: int) -> bool:
@@ -677,14 +819,17 @@ def decode_splits(batch: int, n_kv: int, max_kv_len: int, window: int, sms: Opti
 def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                          k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor, *, ring: int,
                          page_size: int, n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int,
-                         batch: int, n_splits: int, scratch: Optional[tuple] = None) -> None:
+                         batch: int, n_splits: int, scratch: Optional[tuple] = None,
+                         sink: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention of one new token per sequence over the paged cache
     (bfloat16, head_dim <= 256, group <= 16, pages of 64 keys).  With more than
     one split the partial results go through float32 scratch: ``scratch`` =
     (part_o [batch * n_q * n_splits * head_dim], part_ml [batch * n_q * n_splits * 2]),
     made here when it is not given.  ``cu_q``, ``kv_len`` and ``page_table`` are read before the kernel
     waits for the launch before it (they are the host's description of the step, copied in before the
-    step's first kernel); ``q`` and the pages are read after."""
+    step's first kernel); ``q`` and the pages are read after.  ``v_pages`` may be ``k_pages`` itself
+    (the cached row is key and value at once): a tile is then fetched once."""
+    _check_sink(sink, n_kv * group)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k_pages.dtype == torch.bfloat16
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k_pages.is_contiguous() and v_pages.is_contiguous()
     assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
@@ -701,10 +846,11 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
             assert part_o.numel() >= n * head_dim and part_ml.numel() >= n * 2
     f = _fn("attn_mma", "brolm_attn_decode_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                  c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+                                                  c_float, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                  c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k_pages), _ptr(v_pages),
              _ptr(page_table), page_table.stride(0), ring, page_size, n_kv, group, head_dim, scale, cap, window,
-             batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attention_decode_mma")
+             _ptr(sink), batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attention_decode_mma")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -725,7 +871,9 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
              _ptr(streams), counter, _ptr(out), _stream()), "sample")
 
 
-__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale", "rmsnorm", "residual_rmsnorm",
+__all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale",
+           "embed_pairs", "concat_cast", "latent_rows", "route_topk", "group_tiles", "group_pairs", "heads_linear",
+           "experts_linear", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample"]

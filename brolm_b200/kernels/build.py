@@ -41,6 +41,8 @@ LIBRARIES: dict[str, list[str]] = {
     "attn_tc": ["attn_tc.cu"],
     "gemm_stream": ["gemm_stream.cu"],
     "sampling": ["sampling.cu"],
+    "latent": ["latent.cu"],
+    "grouped": ["grouped.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
 

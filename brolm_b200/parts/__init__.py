@@ -1,12 +1,16 @@
 from .attention import Attention
 from .base import ParamSpec, Part, PartSpec, part_class, register_part, registered_parts
-from .block import Block, BlockSpec
+from .block import Block, BlockSpec, ParallelBlock
+from .experts import RoutedExperts
 from .feedforward import GatedFeedForward
-from .layout import EmbeddingSpec, HeadSpec, LayerCall, ModelLayout
+from .latent_attention import LatentAttention
+from .layout import EmbeddingSpec, HeadSpec, LayerCall, ModelLayout, PairTableSpec
 from .linear import linear
 from .norm import RMSNorm, add_then_norm
 from .position import RotaryEmbedding
+from .stream import ConcatLinear
 
 __all__ = ["Attention", "ParamSpec", "Part", "PartSpec", "part_class", "register_part", "registered_parts", "Block",
            "BlockSpec", "GatedFeedForward", "EmbeddingSpec", "HeadSpec", "LayerCall", "ModelLayout", "linear",
-           "RMSNorm", "add_then_norm", "RotaryEmbedding"]
+           "RMSNorm", "add_then_norm", "RotaryEmbedding", "ParallelBlock", "RoutedExperts", "LatentAttention",
+           "PairTableSpec", "ConcatLinear"]

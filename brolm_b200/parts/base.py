@@ -1,8 +1,9 @@
 """What every part of a layer is: a named kind, parameters with declared
 shapes, and a registry so that a layout can ask for a part by name.
 
-Kinds: ``mixer`` (attention here), ``feedforward``, ``norm``, ``position`` and
-``block`` (the arrangement of the others around the residual stream).
+Kinds: ``mixer``, ``feedforward``, ``norm``, ``position``, ``block`` (the
+arrangement of the others around the residual stream) and ``stream`` (a step
+on the residual stream itself between two layers).
 A part gets its sizes and constants as constructor arguments and never learns
 which model it sits in; the checkpoint names of its tensors are given to it by
 the layout, per instance.
@@ -14,7 +15,7 @@ from typing import Any, Optional
 
 import torch
 
-KINDS = ("mixer", "feedforward", "norm", "position", "block")
+KINDS = ("mixer", "feedforward", "norm", "position", "block", "stream")
 
 
 @dataclasses.dataclass(frozen=True)

@@ -93,3 +93,41 @@ class Block(Part):
 
 
 register_part("block", "sandwich", Block)
+
+
+class ParallelBlock(Part):
+    """h += mixer(n1(h)) + ffn(n2(h)): both sublayers read the same stream, each through a norm of its own,
+    and the stream takes both results at once.  Without a feed-forward it is h += mixer(n1(h))."""
+
+    kind = "block"
+
+    def __init__(self, mixer: Part, pre_mixer_norm: Part, feedforward: Optional[Part] = None,
+                 pre_ffn_norm: Optional[Part] = None):
+        if (feedforward is None) != (pre_ffn_norm is None):
+            raise ValueError("block: a feed-forward and its norm come together")
+        self.mixer, self.feedforward = mixer, feedforward
+        self.pre_mixer_norm, self.pre_ffn_norm = pre_mixer_norm, pre_ffn_norm
+
+    def parts(self) -> dict[str, Optional[Part]]:
+        return {"mixer": self.mixer, "feedforward": self.feedforward, "pre_mixer_norm": self.pre_mixer_norm,
+                "pre_ffn_norm": self.pre_ffn_norm}
+
+    @property
+    def entry_norm(self) -> Optional[Part]:
+        return self.pre_mixer_norm
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, h: torch.Tensor, x: torch.Tensor, ctx, entry, writes_cache: bool,
+                next_norm: Optional[Part]) -> Optional[torch.Tensor]:
+        if self.feedforward is None:
+            return add_then_norm(h, self.mixer.forward(x, ctx, entry, writes_cache), None, next_norm, ctx.dtype)
+        x2 = self.pre_ffn_norm.apply(h, ctx.dtype)            # of the stream as the layer found it
+        y = self.mixer.forward(x, ctx, entry, writes_cache)
+        y2 = self.feedforward.forward(x2, ctx)
+        add_then_norm(h, y, None, None, ctx.dtype)
+        return add_then_norm(h, y2, None, next_norm, ctx.dtype)
+
+
+register_part("block", "parallel", ParallelBlock)

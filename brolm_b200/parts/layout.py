@@ -15,9 +15,21 @@ from .block import BlockSpec
 class LayerCall:
     """One entry of the schedule: run ``block``.  ``cache_of`` None: the call
     keeps a cache of its own.  ``cache_of`` = j: it reads the cache that
-    schedule entry j wrote in this step and writes none."""
+    schedule entry j wrote in this step and writes none.  ``before``: the residual stream first goes
+    through the named stream part (which also sees the embedding's output)."""
     block: int
     cache_of: Optional[int] = None
+    before: Optional[str] = None   # a part of ``ModelLayout.stream_parts`` that remakes the stream ahead of this call
+
+
+@dataclasses.dataclass
+class PairTableSpec:
+    """A second table added to the embedding, looked up by a hash of (previous token, token):
+    row (prev * mul_prev + token * mul_cur) mod buckets; a sequence's first token takes row ``buckets``."""
+    tensor: str            # checkpoint name, (buckets + 1, hidden)
+    buckets: int
+    mul_prev: int
+    mul_cur: int
 
 
 @dataclasses.dataclass
@@ -26,6 +38,7 @@ class EmbeddingSpec:
     vocab: int
     hidden: int
     scale: float = 1.0     # multiplies the looked-up row, in float32
+    pairs: Optional[PairTableSpec] = None
 
 
 @dataclasses.dataclass
@@ -46,11 +59,14 @@ class ModelLayout:
     max_positions: int = 0            # the architecture's own limit, 0: none
     weight_std: float = 0.02          # random-weights mode: matrices and tables
     norm_std: float = 0.1             # random-weights mode: vectors
+    stream_parts: dict = dataclasses.field(default_factory=dict)   # name -> PartSpec of kind "stream"
 
     def __post_init__(self):
         for i, call in enumerate(self.schedule):
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names block {call.block} of {len(self.blocks)}")
+            if call.before is not None and call.before not in self.stream_parts:
+                raise ValueError(f"schedule entry {i} names the stream part '{call.before}', which the layout lacks")
             if call.cache_of is not None:
                 j = call.cache_of
                 if not 0 <= j < i or self.schedule[j].cache_of is not None:
