@@ -16,6 +16,12 @@ one prefill step, then decode steps of the 16 sequences (K defaults to 128).
 ``--size 27b``: Gemma 2 27B sizes, a prompt of 2,048 tokens and decoding at
 batch 8 (headline) and batch 1 (a point).  Same JSON shape.
 
+``--arch banevik [--size s|m]``: the Banevik design (latent attention with a window and a sink, routed
+experts, a looped span of layers) at layer sizes of a real model, beside a Gemma 2 model of the same
+width, heads, window, layer runs and active feed-forward size: one prompt of 2,048 tokens and decoding at
+batch 8, both through the engine, and a table of the device time of each kernel of both models with the
+main kernels' fractions of their rooflines.  One JSON line of its own shape; the default run is untouched.
+
 More than one GPU is not what this library does: ``--gpus N`` with N > 1 says
 so and exits with 2.
 """
@@ -146,13 +152,189 @@ def prefill_flops(cfg, layers: int, tokens) -> float:
     return linear + attn + 2.0 * cfg.vocab_size * H * len(lengths)
 
 
+# --arch banevik: layer sizes (a cached row of kv_rank + rot_dim = 256 entries, the widest the tensor-core
+# attention kernels take; sixteen heads, the most a decode tile has rows for)
+BANEVIK_SIZES = {
+    "s": dict(width=2048, heads=16, dim=64, rot_dim=64, vdim=64, kv_rank=192, window=1024, experts=32, top=4,
+              ff=1024, layers=4, loop=(1, 3, 2), vocab=32768),
+    "m": dict(width=3072, heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=192, window=2048, experts=64, top=6,
+              ff=1024, layers=4, loop=(1, 3, 2), vocab=65536),
+}
+
+
+def banevik_main(args, pk) -> int:
+    import torch
+
+    import brolm_b200 as bb
+    from brolm_b200 import kernels
+    from brolm_b200.kernels.microbench import _cuda_events
+
+    z = BANEVIK_SIZES[args.size if args.size in BANEVIK_SIZES else "s"]
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    layer = dict(type="latent_attention",
+                 mixer=dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot_dim"], vdim=z["vdim"], kv_rank=z["kv_rank"],
+                            scale=(z["dim"] + z["rot_dim"]) ** -0.5, rot=dict(base=10000.0, dims=z["rot_dim"]),
+                            mask=dict(size=z["window"])),
+                 mlp=dict(kind="moe", expert=dict(ff=z["ff"]), router=dict(experts=z["experts"], top=z["top"])))
+    bcfg = bb.BanevikConfig.from_dict(dict(
+        architecture="Banevik", vocab=z["vocab"], width=z["width"], layers=[layer] * z["layers"],
+        loop=dict(start=z["loop"][0], stop=z["loop"][1], times=z["loop"][2]), norm=dict(eps=1e-5),
+        embedding=dict(bigram=dict(buckets=65521, mul_prev=8191, mul_cur=127)), logit_softcap=30.0))
+    runs = len(bcfg.runs())
+    inter = (2 * z["top"] * z["ff"] // 3 + 255) // 256 * 256          # three matrices there, two per expert here
+    gcfg = bb.Gemma2Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=inter,
+                           num_hidden_layers=runs, num_attention_heads=z["heads"], num_key_value_heads=z["heads"] // 4,
+                           head_dim=z["dim"] + z["rot_dim"], query_pre_attn_scalar=float(z["dim"] + z["rot_dim"]),
+                           sliding_window=z["window"], layer_types=("sliding_attention",) * runs,
+                           max_position_embeddings=8192)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps, warmup, batch, context, prompt_len = args.steps or 64, max(args.warmup, 3), args.batch or 8, 1280, 2048
+
+    def measure(cfg, vocab):
+        model = bb.Model(cfg, dtype="bfloat16", device=dev).init_random(seed=0, on_device=True)
+        g = torch.Generator().manual_seed(1)
+        out = {}
+        # one prompt, timed alone after an L2 flush: the median of three after three untimed ones
+        eng = bb.Engine(model, max_tokens=prompt_len + 64, max_slots=1, max_seq_len=prompt_len + 1)
+        prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
+        times = []
+        for it in range(6):
+            (s,) = eng.open(1)
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step([s], [prompt])
+            e1.record()
+            torch.cuda.synchronize()
+            eng.close([s])
+            if it >= 3:
+                times.append(e0.elapsed_time(e1))
+
+        def one_prompt():
+            (s,) = eng.open(1)
+            eng.step([s], [prompt])
+            eng.close([s])
+        out["prefill_ms"] = statistics.median(times)
+        out["prefill_kernels"] = _by_kernel(_cuda_events(one_prompt))
+        del eng
+        # decoding: the generation loop's own steps, ids fed on the device
+        total = SETTLE + warmup + steps
+        eng = bb.Engine(model, max_tokens=batch * ((context + 63) // 64 * 64), max_slots=batch, max_seq_len=context + 1)
+        prompts = [torch.randint(0, vocab, (context - total - 1,), generator=g).tolist() for _ in range(batch)]
+        sampler = bb.Sampler(bb.SamplingParams(temperature=0.0))
+        streams = torch.arange(batch, dtype=torch.int32, device=dev)
+        pick = list(range(batch))
+        slots = eng.open(batch)
+        state = {"ids": sampler(eng.step(slots, prompts), streams, 0), "n": 1}
+
+        def go(n):
+            for _ in range(n):
+                state["ids"] = sampler(eng.step_from(slots, state["ids"], pick), streams, state["n"])
+                state["n"] += 1
+        go(SETTLE + warmup)
+        with ClockSampler() as clocks:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            before = kernels.launch_count()
+            e0.record()
+            go(steps)
+            e1.record()
+            torch.cuda.synchronize()
+        out["decode_ms"] = e0.elapsed_time(e1) / steps
+        out["launches"] = kernels.launch_count() - before
+        out["clocks"] = clocks.summary()
+        out["decode_kernels"] = _by_kernel(_cuda_events(lambda: go(1)))
+        eng.close(slots)
+        return out
+
+    b, gm = measure(bcfg, z["vocab"]), measure(gcfg, z["vocab"])
+    W, H, D, R = z["width"], z["heads"], z["kv_rank"] + z["rot_dim"], z["kv_rank"]
+    T, top, ff, win = prompt_len, z["top"], z["ff"], z["window"]
+    keys = win * (win + 1) // 2 + (T - win) * win if T > win else T * (T + 1) // 2
+    hd = z["dim"] + z["rot_dim"]
+    tf, gb = pk["bf16_burst"] * 1e12, pk["hbm_gbs"] * 1e9
+    active = min(z["experts"], batch * top)
+    # (kernel-name fragment, calls per layer run, flops or bytes per call, bound) for the main kernels of both models
+    rows = [
+        ("banevik prefill", b["prefill_kernels"], [
+            ("grouped_bf16", 2, 2.0 * T * top * ff * W, "flops"),
+            ("attn_prefill_mma", 1, 4.0 * H * D * keys, "flops"),
+        ]),
+        ("closest prefill", gm["prefill_kernels"], [
+            ("gemm_tc2", None, 2.0 * T * W * (3 * inter + 2 * H * hd + 2 * (H // 4) * hd), "flops_total"),
+            ("attn_prefill_tc", 1, 4.0 * H * hd * keys, "flops"),
+        ]),
+        ("banevik decode", b["decode_kernels"], [
+            ("grouped_bf16", 2, active * ff * W * 2.0, "bytes"),
+            ("attn_decode_mma", 1, batch * min(context, win) * D * 2.0, "bytes"),
+        ]),
+        ("closest decode", gm["decode_kernels"], [
+            ("skinny_gemm_kernel", None, (3 * inter + 2 * H * hd + 2 * (H // 4) * hd) * W * 2.0, "bytes_total"),
+            ("attn_decode_mma", 1, batch * min(context, win) * 2 * (H // 4) * hd * 2.0, "bytes"),
+        ]),
+    ]
+    table = []
+    for title, kern, wanted in rows:
+        for frag, calls, work, bound in wanted:
+            us = sum(v["us"] for k, v in kern.items() if frag in k)
+            n = sum(v["n"] for k, v in kern.items() if frag in k)
+            if not n:
+                continue
+            per_run = us / runs
+            total_work = work * runs if bound.endswith("total") is False else work * runs
+            frac = total_work / (us * 1e-6) / (tf if bound.startswith("flops") else gb)
+            table.append({"step": title, "kernel": frag, "launches": n, "us_per_layer_run": round(per_run, 2),
+                          "bound": "tensor" if bound.startswith("flops") else "hbm", "frac_of_measured_peak": round(frac, 4)})
+    result = {
+        "metric": f"Banevik decode tokens/s (size {args.size if args.size in BANEVIK_SIZES else 's'}, batch {batch}, "
+                  f"context {context}) beside Gemma 2 at equal sizes",
+        "value": round(batch * 1000.0 / b["decode_ms"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(b["decode_ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "brolm_b200", "clocks": b["clocks"], "gpu_launches": b["launches"],
+        "config": {"model": "Banevik", **{k: v for k, v in z.items()}, "layer_runs": runs, "global_batch": batch,
+                   "seq_len": context, "closest": {"model": "Gemma 2", "hidden": W, "heads": H, "kv_heads": H // 4,
+                                                   "head_dim": hd, "intermediate": inter, "layers": runs,
+                                                   "sliding_window": win},
+                   "l2": "the prompt is timed after an L2 flush; a decode step reads more than the L2 holds",
+                   "peaks": pk["source"]},
+        "banevik": {"prefill_tok_s": round(T * 1000.0 / b["prefill_ms"], 1), "prefill_ms": round(b["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / b["decode_ms"], 1), "decode_ms": round(b["decode_ms"], 4)},
+        "closest": {"prefill_tok_s": round(T * 1000.0 / gm["prefill_ms"], 1), "prefill_ms": round(gm["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / gm["decode_ms"], 1), "decode_ms": round(gm["decode_ms"], 4)},
+        "kernels": table,
+        "by_kernel_us": {"banevik_prefill": _top(b["prefill_kernels"]), "closest_prefill": _top(gm["prefill_kernels"]),
+                         "banevik_decode": _top(b["decode_kernels"]), "closest_decode": _top(gm["decode_kernels"])},
+    }
+    print(json.dumps(result))
+    return 0
+
+
+def _by_kernel(events) -> dict:
+    """Device records -> {kernel name: {"us": total time, "n": launches}}."""
+    out: dict = {}
+    for e in events:
+        name = e.name.replace("void ", "").replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+        name = name.split("(")[0][:60]
+        d = out.setdefault(name, {"us": 0.0, "n": 0})
+        d["us"] += e.time_range.end - e.time_range.start
+        d["n"] += 1
+    return out
+
+
+def _top(kern: dict, n: int = 14) -> dict:
+    return {k: [round(v["us"], 1), v["n"]] for k, v in sorted(kern.items(), key=lambda kv: -kv[1]["us"])[:n]}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik"],
+                    help="banevik: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=0, help="decode steps in a timed region (default 64; 128 for 9b)")
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="brolm_b200")
-    ap.add_argument("--size", default="2b", choices=sorted(SIZES))
+    ap.add_argument("--size", default="2b", choices=sorted(SIZES) + sorted(BANEVIK_SIZES))
     ap.add_argument("--batch", type=int, default=0, help="sequences of the headline run (default: the workload's)")
     ap.add_argument("--context", type=int, default=0,
                     help="tokens a sequence holds after the last timed step (default 8192; 2304 for 27b)")
@@ -168,6 +350,11 @@ def main() -> int:
         return 0
     if args.gpus != 1:
         print(f"bench.py: brolm_b200 is a one-GPU library; --gpus {args.gpus} is not supported")
+        return 2
+    if args.arch == "banevik":
+        return banevik_main(args, peaks())
+    if args.size not in SIZES:
+        print(f"bench.py: --size {args.size} goes with --arch banevik")
         return 2
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)

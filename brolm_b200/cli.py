@@ -1,4 +1,5 @@
-"""run_gemma2: generate from a model folder on one GPU.
+"""run_model (also installed as run_gemma2): generate from a model folder on one GPU, whatever registered
+architecture its config.json names.
 
 Options are named as in wlejon/brolm's text tools
 (tools/run_mistral_text.cpp:63-82): --max-new, --temp (<= 0: greedy, the
@@ -25,7 +26,7 @@ def parse_ids(text: str) -> list[int]:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="run_gemma2", description=__doc__.split("\n\n")[0])
+    ap = argparse.ArgumentParser(prog=os.path.basename(sys.argv[0]) or "run_model", description=__doc__.split("\n\n")[0])
     ap.add_argument("--model", help="folder with config.json and *.safetensors")
     ap.add_argument("--random", action="store_true", help="random weights for the sizes in --config")
     ap.add_argument("--config", help="config.json for --random (default: gemma-2-2b sizes)")
@@ -87,11 +88,13 @@ def main(argv=None) -> int:
             print(f"[load] random weights, seed {args.weights_seed}")
             model = bb.Model(cfg, dtype=args.dtype, device=args.device).init_random(args.weights_seed, on_device=True)
         cfg = model.config
-        print(f"[info] hidden={cfg.hidden_size} layers={cfg.num_hidden_layers} q={cfg.num_attention_heads} "
-              f"kv={cfg.num_key_value_heads} vocab={cfg.vocab_size} dtype={args.dtype}")
+        lay = model.layout
+        print(f"[info] {type(cfg).architecture}: hidden={lay.embedding.hidden} layer runs={len(lay.schedule)} "
+              f"vocab={lay.embedding.vocab} dtype={args.dtype}")
         print(f"[info] weights loaded in {time.time() - t0:.1f} s")
-        if not args.no_bos:
-            prompts = [[cfg.bos_token_id] + p for p in prompts]
+        bos = getattr(cfg, "bos_token_id", None)          # a family without a start token has none to prepend
+        if not args.no_bos and bos is not None:
+            prompts = [[bos] + p for p in prompts]
         batch = args.batch or len(prompts)
         need = sum(sorted(((len(p) + args.max_new + 63) // 64 * 64 for p in prompts), reverse=True)[:batch])
         engine = bb.Engine(model, max_tokens=max(need, 64), max_slots=batch)
@@ -100,7 +103,7 @@ def main(argv=None) -> int:
             sampling=bb.SamplingParams(temperature=args.temp, top_k=args.top_k, top_p=args.top_p, seed=args.seed),
             stop_on_eos=not args.no_eos, stop_ids=tuple(args.stop_id))
         t0 = time.time()
-        outs = bb.generate(engine, prompts, eos_id=cfg.eos_token_id, opts=opts, batch_size=batch)
+        outs = bb.generate(engine, prompts, eos_id=getattr(cfg, "eos_token_id", -1), opts=opts, batch_size=batch)
         dt = time.time() - t0
         for p, o in zip(prompts, outs):
             print(f"[info] prompt tokens: {len(p)}")

@@ -55,6 +55,9 @@ class DecoderModel:
         self.loaded = False
         self.generation = 0          # goes up whenever the tensors a captured step points at are replaced
         self.last_hidden: Optional[torch.Tensor] = None    # the final norm's rows of the last pass
+        # set to a list to receive a copy of the residual stream after every schedule entry of a pass
+        # (for looking into a model; a captured decode step does not fill it)
+        self.keep_streams: Optional[list] = None
 
     # construction ---------------------------------------------------------
     def _build(self, spec: PartSpec) -> Part:
@@ -181,6 +184,8 @@ class DecoderModel:
             if i + 1 < len(sched) and sched[i + 1].before is None:
                 nxt = self.blocks[sched[i + 1].block].entry_norm
             x = blk.forward(h, x, ctx, entry, call.cache_of is None, nxt)
+            if self.keep_streams is not None:
+                self.keep_streams.append(h.clone())
         head_in = torch.float32 if self.head.dtype == torch.float32 else self.dtype
         if rows.numel() == 0:
             self.last_hidden = torch.empty((0, lay.embedding.hidden), dtype=head_in, device=self.device)

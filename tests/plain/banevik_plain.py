@@ -27,7 +27,9 @@ F = torch.float64
 
 def embed(config, w, tokens):
     """Token rows plus the rows of the bigram table."""
-    bg = config["embedding"]["bigram"]
+    bg = (config.get("embedding") or {}).get("bigram")
+    if bg is None:
+        return torch.stack([w["embed"][tok].to(F) for tok in tokens])
     rows = []
     for t, tok in enumerate(tokens):
         if t == 0:
@@ -47,16 +49,14 @@ def norm(x, weight, eps):
 
 
 def rotate(x, positions, base, dims):
-    """x [T, n]: the first ``dims`` entries are rotated as pairs (i, i + dims/2); the rest pass."""
+    """x [T, n]: the first ``dims`` entries turn as pairs (i, i + dims/2) by position * base^(-2i/dims); the rest pass."""
+    if dims == 0:
+        return x.clone()
     half = dims // 2
-    out = x.clone()
-    for t, p in enumerate(positions):
-        for i in range(half):
-            a = p * base ** (-2.0 * i / dims)
-            u, v = x[t, i], x[t, i + half]
-            out[t, i] = u * math.cos(a) - v * math.sin(a)
-            out[t, i + half] = v * math.cos(a) + u * math.sin(a)
-    return out
+    freq = torch.tensor([base ** (-2.0 * i / dims) for i in range(half)], dtype=F)
+    a = torch.tensor(list(positions), dtype=F)[:, None] * freq[None, :]
+    u, v = x[:, :half], x[:, half:dims]
+    return torch.cat([u * a.cos() - v * a.sin(), v * a.cos() + u * a.sin(), x[:, dims:]], dim=1)
 
 
 def latent_attention(m, w, pre, h, eps):
@@ -85,13 +85,19 @@ def latent_attention(m, w, pre, h, eps):
     return out.reshape(T, H * dv) @ w[pre + "o"].to(F).T
 
 
-def experts(m, w, pre, h):
-    """Routed feed-forward; h [T, D] -> [T, D].  ``pre``: 'l3.mlp.'."""
+def experts(m, w, pre, h, margins=None):
+    """Routed feed-forward; h [T, D] -> [T, D].  ``pre``: 'l3.mlp.'.  ``margins``: a list that receives, per
+    token, how far the last chosen score is above the first one left out, relative to the largest |z|
+    (infinite when every expert is chosen): a rounded run may choose otherwise where this is tiny."""
     E, top = m["router"]["experts"], m["router"]["top"]
-    s = torch.sigmoid(h @ w[pre + "router"].to(F).T)
+    z = h @ w[pre + "router"].to(F).T
+    s = torch.sigmoid(z)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         chosen = torch.topk(s[t], top).indices.tolist()
+        if margins is not None:
+            zs = torch.sort(z[t], descending=True).values
+            margins.append(float("inf") if top == E else float((zs[top - 1] - zs[top]) / z[t].abs().max()))
         for e in chosen:
             x = s[t, e] * h[t]
             u = torch.relu(w[f"{pre}e{e}.up"].to(F) @ x) ** 2
