@@ -257,19 +257,19 @@ def banevik_main(args, pk) -> int:
     # (kernel-name fragment, calls per layer run, flops or bytes per call, bound) for the main kernels of both models
     rows = [
         ("banevik prefill", b["prefill_kernels"], [
-            ("grouped_bf16", 2, 2.0 * T * top * ff * W, "flops"),
+            ("fast_kernel<128, 32, 4, false>", 2, 2.0 * T * top * ff * W * 2, "flops"),
             ("attn_prefill_mma", 1, 4.0 * H * D * keys, "flops"),
         ]),
         ("closest prefill", gm["prefill_kernels"], [
-            ("gemm_tc2", None, 2.0 * T * W * (3 * inter + 2 * H * hd + 2 * (H // 4) * hd), "flops_total"),
+            ("gemm_tc2_kernel<1>", 1, 2.0 * T * W * 2 * inter, "flops"),
             ("attn_prefill_tc", 1, 4.0 * H * hd * keys, "flops"),
         ]),
         ("banevik decode", b["decode_kernels"], [
-            ("grouped_bf16", 2, active * ff * W * 2.0, "bytes"),
+            ("fast_kernel<64, 64, 4, false>", 2, active * ff * W * 2.0 * 2, "bytes"),
             ("attn_decode_mma", 1, batch * min(context, win) * D * 2.0, "bytes"),
         ]),
         ("closest decode", gm["decode_kernels"], [
-            ("skinny_gemm_kernel", None, (3 * inter + 2 * H * hd + 2 * (H // 4) * hd) * W * 2.0, "bytes_total"),
+            ("skinny_kernel<2, 1, 1>", 1, 2 * inter * W * 2.0, "bytes"),
             ("attn_decode_mma", 1, batch * min(context, win) * 2 * (H // 4) * hd * 2.0, "bytes"),
         ]),
     ]
@@ -281,7 +281,7 @@ def banevik_main(args, pk) -> int:
             if not n:
                 continue
             per_run = us / runs
-            total_work = work * runs if bound.endswith("total") is False else work * runs
+            total_work = work * runs                       # (work: of all the kernel's launches in one layer run)
             frac = total_work / (us * 1e-6) / (tf if bound.startswith("flops") else gb)
             table.append({"step": title, "kernel": frag, "launches": n, "us_per_layer_run": round(per_run, 2),
                           "bound": "tensor" if bound.startswith("flops") else "hbm", "frac_of_measured_peak": round(frac, 4)})
@@ -315,7 +315,7 @@ def _by_kernel(events) -> dict:
     out: dict = {}
     for e in events:
         name = e.name.replace("void ", "").replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
-        name = name.split("(")[0][:60]
+        name = name.split("(")[0][:72]
         d = out.setdefault(name, {"us": 0.0, "n": 0})
         d["us"] += e.time_range.end - e.time_range.start
         d["n"] += 1

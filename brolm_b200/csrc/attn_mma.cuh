@@ -567,6 +567,8 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
         // up to four splits: a thread fetches the statistics of its row's splits and its four outputs of
         // every split at once and merges them by itself: one round trip to the L2, no exchange
         const int q4 = hd >> 2;
+        // (with many heads on one kv head a thread has several rounds: their loads are issued together)
+#pragma unroll 4
         for (int idx = threadIdx.x; idx < a.group * q4; idx += NTHREADS) {
             const int row = idx / q4, d = (idx - row * q4) * 4;
             const size_t slot0 = ((size_t)b * n_q + g * a.group + row) * a.n_splits;

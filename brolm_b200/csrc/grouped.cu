@@ -8,7 +8,8 @@
 //
 // float operands run on CUDA cores, every output the fma sum over k in
 // ascending order; bfloat16 operands run on the tensor cores (mma.sync
-// m16n8k16, float accumulation).  An output depends on its own row alone, so
+// m16n8k16, float accumulation; a pipelined kernel for operands whose rows
+// start on 16-byte borders, a plain one for all others).  An output depends on its own row alone, so
 // a token gives the same bits whatever else is in the batch.
 #include "common.cuh"
 
@@ -18,45 +19,114 @@ constexpr int GBM = 64, GBN = 64;
 
 // ---------------------------------------------------------------------------
 // Router: z = Wr x in float, the `top` largest z (ties: the lower index), weight
-// f(z) with f = logistic function.  One block per token.
+// f(z) with f = logistic function.  A block takes RT tokens (one when there are
+// few, so that more SMs take part; four when there are many, so that a row of
+// Wr is fetched once for four tokens); a warp takes an expert at a time for all
+// of the block's tokens.  A (token, expert) sum is the lanes' strided partial
+// sums, added by one fixed tree: it does not depend on what else is in the block.
 // ---------------------------------------------------------------------------
-template <typename T>
+template <typename T, int RT>
 __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ wr,
-                                                    int E, int D, int top, int32_t* __restrict__ ids,
-                                                    float* __restrict__ wts) {
-    extern __shared__ float z[];                       // [E]
-    const int t = blockIdx.x;
+                                                    int E, int D, int top, int tokens, int vec,
+                                                    int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float z[];                       // [RT][E]
+    const int t0 = blockIdx.x * RT;
+    const int nt = min(RT, tokens - t0);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const T* xr = x + (size_t)t * ldx;
     for (int e = warp; e < E; e += nwarps) {
         const T* w = wr + (size_t)e * D;
-        float s = 0.0f;
-        for (int i = lane; i < D; i += 32) s = fmaf(to_float(xr[i]), to_float(w[i]), s);
-        s = warp_sum(s);
-        if (lane == 0) z[e] = s;
-    }
-    __syncthreads();
-    if (warp != 0) return;
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int at = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = z[e];
-            if (v > best || (v == best && e < at)) { best = v; at = e; }
+        float acc[RT];
+#pragma unroll
+        for (int r = 0; r < RT; ++r) acc[r] = 0.0f;
+        if (vec) {
+            // U chunks of the expert's row in flight per lane ahead of the first use
+            constexpr int U = RT == 1 ? 8 : 2;
+            for (int i0 = lane * 8; i0 < D; i0 += 256 * U) {
+                if constexpr (sizeof(T) == 4) {             // float rows: a chunk of eight is two 16-byte loads
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int i = i0 + u * 256;
+                        if (i < D) {
+                            float wv[8];
+                            load8(w + i, wv);
+#pragma unroll
+                            for (int r = 0; r < RT; ++r)
+                                if (r < nt) {
+                                    float xv[8];
+                                    load8(x + (size_t)(t0 + r) * ldx + i, xv);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) acc[r] = fmaf(xv[j], wv[j], acc[r]);
+                                }
+                        }
+                    }
+                } else {
+                uint4 wq[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    wq[u] = i0 + u * 256 < D ? *reinterpret_cast<const uint4*>(w + i0 + u * 256) : make_uint4(0u, 0u, 0u, 0u);
+                uint4 xq[RT][U];
+#pragma unroll
+                for (int r = 0; r < RT; ++r)
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        xq[r][u] = (r < nt && i0 + u * 256 < D)
+                                       ? *reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * ldx + i0 + u * 256)
+                                       : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const __nv_bfloat162* hw = reinterpret_cast<const __nv_bfloat162*>(&wq[u]);
+#pragma unroll
+                    for (int r = 0; r < RT; ++r) {
+                        const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&xq[r][u]);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 a = __bfloat1622float2(hx[j]), b = __bfloat1622float2(hw[j]);
+                            acc[r] = fmaf(a.x, b.x, acc[r]);
+                            acc[r] = fmaf(a.y, b.y, acc[r]);
+                        }
+                    }
+                }
+                }
+            }
+        } else {
+            for (int i = lane; i < D; i += 32) {
+                const float wv = to_float(w[i]);
+#pragma unroll
+                for (int r = 0; r < RT; ++r)
+                    if (r < nt) acc[r] = fmaf(to_float(x[(size_t)(t0 + r) * ldx + i]), wv, acc[r]);
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        for (int r = 0; r < RT; ++r) {
+            const float s = warp_sum(acc[r]);
+            if (lane == 0) z[r * E + e] = s;
         }
-        if (at >= E) at = 0;                           // (every score was -inf or NaN)
-        if (lane == 0) {
-            ids[(size_t)t * top + k] = at;
-            wts[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
-            z[at] = -INFINITY;
+    }
+    __syncthreads();
+    for (int r = warp; r < nt; r += nwarps) {          // a warp picks for a token
+        float* zr = z + r * E;
+        const int t = t0 + r;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float v = zr[e];
+                if (v > best || (v == best && e < at)) { best = v; at = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (at >= E) at = 0;                       // (every score was -inf or NaN)
+            if (lane == 0) {
+                ids[(size_t)t * top + k] = at;
+                wts[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+                zr[at] = -INFINITY;
+            }
+            __syncwarp();
         }
-        __syncwarp();
     }
 }
 
@@ -374,7 +444,130 @@ __global__ void __launch_bounds__(128) grouped_bf16_kernel(GroupedArgs g, int ve
         }
 }
 
-int launch_grouped(int dtype, GroupedArgs& g, int row_tiles, cudaStream_t stream) {
+// --- bfloat16, operands whose rows start on 16-byte borders: eight warps, 64 rows x FBN outputs a block, the tiles of A
+// and W through a ring of cp.async stages; the gate of a pair is applied to the float sums ahead of the activation:
+// act(g * (W x)), which is W (g x) without rounding g x to bfloat16 first.  Two shapes of the ring: four stages of
+// 32 k (60 KB, three blocks to an SM) when the groups have many rows and the tensor cores set the pace; six stages of
+// 64 k (162 KB, 80 KB of W in flight per block) when a group has a handful of rows (decoding) and the kernel is a
+// stream of the matrices: with about one block per SM that is what it takes against the memory's latency.
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+// (HEADS only tells the per-head products from the experts' in a profile: the code is the same)
+template <int FBN, int BK, int STAGES, bool HEADS>
+__global__ void __launch_bounds__(256) grouped_bf16_fast_kernel(GroupedArgs g) {
+    constexpr int LD = BK + 8, CPR = BK / 8, WN = FBN / 4, NP = WN / 16;   // a warp: 32 rows x WN outputs
+    extern __shared__ __align__(128) unsigned char fsm[];
+    __shared__ RowInfo info[GBM];
+    const int group = tile_rows(g, blockIdx.y, info);
+    if (group < 0) return;
+    __syncthreads();
+    bf16* As = reinterpret_cast<bf16*>(fsm);                       // [STAGES][GBM][LD]
+    bf16* Bs = As + STAGES * GBM * LD;                             // [STAGES][FBN][LD]
+    const uint32_t as_base = smem_addr(As), bs_base = smem_addr(Bs);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = (warp >> 2) * 32, wn = (warp & 3) * WN;
+    const int n0 = blockIdx.x * FBN;
+    const bf16* A = (const bf16*)g.a;
+    const bf16* W = (const bf16*)g.w + (size_t)group * g.w_goff;
+    auto load_stage = [&](int stage, int kb) {                     // (K is a multiple of 8: a chunk is whole or absent)
+#pragma unroll
+        for (int i = 0; i < GBM * CPR / 256; ++i) {
+            const int c = tid + i * 256, row = c / CPR, kc = (c % CPR) * 8, k = kb * BK + kc;
+            const bool ok = info[row].valid && k < g.K;
+            cp_async_16(as_base + (uint32_t)((stage * GBM + row) * LD + kc) * 2u, A + (ok ? info[row].a_off + k : 0),
+                        ok ? 16 : 0);
+        }
+#pragma unroll
+        for (int i = 0; i < FBN * CPR / 256; ++i) {
+            const int c = tid + i * 256, row = c / CPR, kc = (c % CPR) * 8, k = kb * BK + kc;
+            const bool ok = n0 + row < g.N && k < g.K;
+            cp_async_16(bs_base + (uint32_t)((stage * FBN + row) * LD + kc) * 2u,
+                        W + (ok ? (size_t)(n0 + row) * g.ldw + k : 0), ok ? 16 : 0);
+        }
+    };
+    float acc[2][2 * NP][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2 * NP; ++j) { acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f; }
+    const int nk = (g.K + BK - 1) / BK;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < nk) load_stage(s, s);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    const uint32_t a_frag = as_base + (uint32_t)((wm + (lane & 15)) * LD + (lane >> 4) * 8) * 2u;
+    const uint32_t b_frag = bs_base + (uint32_t)((wn + (lane & 7) + ((lane >> 4) << 3)) * LD + ((lane >> 3) & 1) * 8) * 2u;
+    for (int kb = 0; kb < nk; ++kb) {
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2) : "memory");
+        __syncthreads();                                   // stage kb has landed; everyone is done with stage kb - 1
+        if (kb + STAGES - 1 < nk) load_stage((kb + STAGES - 1) % STAGES, kb + STAGES - 1);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const uint32_t sa = a_frag + (uint32_t)(kb % STAGES) * GBM * LD * 2u;
+        const uint32_t sb = b_frag + (uint32_t)(kb % STAGES) * FBN * LD * 2u;
+#pragma unroll
+        for (int ks = 0; ks < BK; ks += 16) {
+            uint32_t af[2][4], bfr[NP][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+                ldsm_x4(sa + (uint32_t)(mt * 16 * LD + ks) * 2u, af[mt][0], af[mt][1], af[mt][2], af[mt][3]);
+#pragma unroll
+            for (int np = 0; np < NP; ++np)
+                ldsm_x4(sb + (uint32_t)(np * 16 * LD + ks) * 2u, bfr[np][0], bfr[np][1], bfr[np][2], bfr[np][3]);
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int np = 0; np < NP; ++np) {
+                    mma16816(acc[mt][2 * np], af[mt], bfr[np][0], bfr[np][1]);
+                    mma16816(acc[mt][2 * np + 1], af[mt], bfr[np][2], bfr[np][3]);
+                }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const RowInfo ri = info[wm + mt * 16 + (lane >> 2) + 8 * half];
+            if (!ri.valid) continue;
+#pragma unroll
+            for (int nt = 0; nt < 2 * NP; ++nt) {
+                const int n = n0 + wn + nt * 8 + (lane & 3) * 2;
+                const float v0 = act_of(acc[mt][nt][2 * half] * ri.scale, g.act);
+                const float v1 = act_of(acc[mt][nt][2 * half + 1] * ri.scale, g.act);
+                if (g.out_f32) {
+                    float* o = (float*)g.out + ri.o_off + n;
+                    if (n < g.N) o[0] = v0;
+                    if (n + 1 < g.N) o[1] = v1;
+                } else {
+                    bf16* o = (bf16*)g.out + ri.o_off + n;
+                    if (n < g.N) o[0] = __float2bfloat16_rn(v0);
+                    if (n + 1 < g.N) o[1] = __float2bfloat16_rn(v1);
+                }
+            }
+        }
+}
+
+template <int FBN, int BK, int STAGES, bool HEADS>
+int launch_fast(const GroupedArgs& g, int row_tiles, cudaStream_t stream) {
+    constexpr int smem = STAGES * (GBM + FBN) * (BK + 8) * 2;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(grouped_bf16_fast_kernel<FBN, BK, STAGES, HEADS>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        raised = true;
+    }
+    dim3 grid((g.N + FBN - 1) / FBN, row_tiles);
+    grouped_bf16_fast_kernel<FBN, BK, STAGES, HEADS><<<grid, 256, smem, stream>>>(g);
+    return launch_status();
+}
+
+// `few`: the groups have a handful of rows each (decoding), so the matrices are streamed rather than tiled
+int launch_grouped(int dtype, GroupedArgs& g, int row_tiles, bool few, cudaStream_t stream) {
     if (g.N <= 0 || row_tiles <= 0) return BROLM_OK;
     if (g.K <= 0) return BROLM_ERR_BAD_SIZE;
     if (row_tiles > 65535) return BROLM_ERR_TOO_LARGE;
@@ -385,7 +578,15 @@ int launch_grouped(int dtype, GroupedArgs& g, int row_tiles, cudaStream_t stream
     } else if (dtype == BROLM_BF16) {
         const int vec = g.K % 8 == 0 && g.lda % 8 == 0 && g.a_goff % 8 == 0 && g.ldw % 8 == 0 && g.w_goff % 8 == 0 &&
                         ((uintptr_t)g.a & 15) == 0 && ((uintptr_t)g.w & 15) == 0;
-        grouped_bf16_kernel<<<grid, 128, 0, stream>>>(g, vec);
+        if (vec) {
+            if (g.mode == MODE_HEADS)
+                return few ? launch_fast<64, 64, 4, true>(g, row_tiles, stream)
+                           : launch_fast<128, 32, 4, true>(g, row_tiles, stream);
+            return few ? launch_fast<64, 64, 4, false>(g, row_tiles, stream)
+                       : launch_fast<128, 32, 4, false>(g, row_tiles, stream);
+        } else {
+            grouped_bf16_kernel<<<grid, 128, 0, stream>>>(g, 0);
+        }
     } else {
         return BROLM_ERR_BAD_DTYPE;
     }
@@ -400,15 +601,22 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
     if (tokens <= 0) return BROLM_OK;
     if (experts <= 0 || top <= 0 || top > experts || width <= 0) return BROLM_ERR_BAD_SIZE;
     if (experts > 8192) return BROLM_ERR_TOO_LARGE;
-    const size_t smem = (size_t)experts * sizeof(float);
-    if (dtype == BROLM_F32)
-        route_kernel<float><<<tokens, 256, smem, stream>>>((const float*)x, ldx, (const float*)wr, experts, width, top,
-                                                           (int32_t*)ids, (float*)wts);
-    else if (dtype == BROLM_BF16)
-        route_kernel<bf16><<<tokens, 256, smem, stream>>>((const bf16*)x, ldx, (const bf16*)wr, experts, width, top,
-                                                          (int32_t*)ids, (float*)wts);
-    else
+    const int vec = width % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)wr & 15) == 0;
+    const bool many = tokens > 64 && experts <= 1024;      // (four rows of scores in the default shared memory)
+    const int rt = many ? 4 : 1;
+    const size_t smem = (size_t)rt * experts * sizeof(float);
+    const int blocks = (tokens + rt - 1) / rt;
+#define BROLM_ROUTE(T, RT)                                                                                        \
+    route_kernel<T, RT><<<blocks, 256, smem, stream>>>((const T*)x, ldx, (const T*)wr, experts, width, top, tokens, \
+                                                       vec, (int32_t*)ids, (float*)wts)
+    if (dtype == BROLM_F32) {
+        if (many) BROLM_ROUTE(float, 4); else BROLM_ROUTE(float, 1);
+    } else if (dtype == BROLM_BF16) {
+        if (many) BROLM_ROUTE(bf16, 4); else BROLM_ROUTE(bf16, 1);
+    } else {
         return BROLM_ERR_BAD_DTYPE;
+    }
+#undef BROLM_ROUTE
     return launch_status();
 }
 
@@ -436,13 +644,13 @@ BROLM_API int brolm_heads_linear(int dtype, const void* a, long lda, long a_goff
     g.N = N; g.K = K; g.mode = MODE_HEADS; g.rows = rows; g.tiles_per_group = (rows + GBM - 1) / GBM;
     const long long tiles = (long long)g.tiles_per_group * groups;
     if (tiles > 65535) return BROLM_ERR_TOO_LARGE;
-    return launch_grouped(dtype, g, (int)tiles, stream);
+    return launch_grouped(dtype, g, (int)tiles, rows <= 8, stream);
 }
 
 // Experts, first product: u[s, :] = act(W[e] (scale[p] * x[token of p, :])) for the s-th pair p of the expert
 // order.  Second product (down != 0): out[choice of p][token of p][:] = W[e] u[s, :], float.
 BROLM_API int brolm_experts_linear(int dtype, int down, const void* a, long lda, const void* w, long ldw, long w_goff,
-                                   void* out, long ldo, int out_f32, int act, int N, int K, const void* tile_group,
+                                   int groups, void* out, long ldo, int out_f32, int act, int N, int K, const void* tile_group,
                                    const void* tile_row0, const void* offsets, const void* perm, const void* scale,
                                    int top, int tokens, int max_tiles, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
@@ -452,5 +660,5 @@ BROLM_API int brolm_experts_linear(int dtype, int down, const void* a, long lda,
     g.tile_group = (const int32_t*)tile_group; g.tile_row0 = (const int32_t*)tile_row0;
     g.offsets = (const int32_t*)offsets; g.perm = (const int32_t*)perm; g.scale = (const float*)scale;
     g.top = top; g.tokens = tokens;
-    return launch_grouped(dtype, g, max_tiles, stream);
+    return launch_grouped(dtype, g, max_tiles, (long)tokens * top <= 8L * groups, stream);
 }

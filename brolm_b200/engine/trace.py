@@ -25,11 +25,16 @@ from .model import load_model
 from .step import Engine
 
 
+SPARE_PAGES = 64        # room for the partly filled last pages of the live requests
+
+
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[str], device: str = "cuda:0",
            log: IO[str] = sys.stdout) -> None:
     os.makedirs(out_dir, exist_ok=True)
     model = load_model(model_dir, dtype=dtype, device=device)
-    engine = Engine(model, max_tokens=max_tokens)
+    # the cache hands out whole pages: every live request may end in one that is partly filled
+    page = 64
+    engine = Engine(model, max_tokens=(max_tokens + page - 1) // page * page + SPARE_PAGES * page)
     slot_of: dict[str, int] = {}
     for line in lines:
         line = line.strip()
@@ -64,7 +69,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", required=True, type=int,
-                    help="most tokens live requests hold at one time (each rounded up to a multiple of 64)")
+                    help="most tokens live requests hold at one time (the cache adds room for 64 partly filled pages)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, args.device)

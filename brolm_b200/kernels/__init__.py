@@ -348,10 +348,10 @@ def experts_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, per
         assert tuple(out.shape) == (pairs, N) and a.shape[0] == tokens and out.dtype in (torch.float32, a.dtype)
     if activation not in EXPERT_ACTS:
         raise KernelError(f"experts_linear: unknown activation '{activation}' (known: {sorted(EXPERT_ACTS)})")
-    f = _fn("grouped", "brolm_experts_linear", [c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_long, c_void_p, c_long,
+    f = _fn("grouped", "brolm_experts_linear", [c_int, c_int, c_void_p, c_long, c_void_p, c_long, c_long, c_int, c_void_p, c_long,
                                                 c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_code(a), 1 if down else 0, _ptr(a), a.stride(0), _ptr(weight), K, N * K, _ptr(out), N,
+    _check(f(_code(a), 1 if down else 0, _ptr(a), a.stride(0), _ptr(weight), K, N * K, E, _ptr(out), N,
              1 if out.dtype == torch.float32 else 0, EXPERT_ACTS[activation], N, K, _ptr(tiles[0]), _ptr(tiles[1]),
              _ptr(offsets), _ptr(perm), _ptr(scale), top, tokens, tiles.shape[1], _stream()), "experts_linear")
 

@@ -108,6 +108,10 @@ class LatentAttention(Part):
         elif tensor_cores and ctx.mode == "decode" and page == 64 and H <= 16:
             splits = kernels.decode_splits(ctx.batch, 1, ctx.max_kv_len, self.window or 0,
                                            ragged=getattr(ctx, "ragged", False))
+            if H * D >= 2048:
+                # every split leaves H * D floats for the block that merges them; up to four are merged in one
+                # round trip, and with all heads on one cached row a split is cheap to run and dear to merge
+                splits = min(splits, 4)
             kernels.attention_decode_mma(q, out, ctx.cu_q, ctx.kv_len, pages, pages, table, ring=ring, page_size=page,
                                          n_splits=splits, **common)
         else:

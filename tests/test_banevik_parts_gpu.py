@@ -93,9 +93,10 @@ def test_router(dtype, E, top, D):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,E,top,D,F", [(1, 4, 2, 32, 16), (7, 6, 1, 40, 24), (70, 3, 3, 48, 40), (300, 5, 2, 36, 20),
-                                         (3, 9, 1, 64, 72)])
+                                         (3, 9, 1, 64, 72), (300, 4, 2, 64, 136), (5, 8, 2, 64, 72), (40, 2, 1, 128, 64)])
 def test_routed_experts_part(dtype, T, E, top, D, F):
-    """Experts with many rows (several tiles), with one row, with none; sizes that are no multiples of 8."""
+    """Experts with many rows (several tiles), with one row, with none; sizes that are no multiples of 8 (the plain
+    kernel), aligned sizes with many rows (the pipelined kernel) and with a few (the streaming kernel)."""
     part = RoutedExperts(D, F, E, top)
     g = torch.Generator().manual_seed(T)
     ws = {n: (torch.randn(s.shape, generator=g) * (1.0 if n == "router" else 0.25)).to(dtype)
