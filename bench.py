@@ -257,6 +257,7 @@ def banevik_main(args, pk) -> int:
     # (kernel-name fragment, calls per layer run, flops or bytes per call, bound) for the main kernels of both models
     rows = [
         ("banevik prefill", b["prefill_kernels"], [
+            ("grouped_tc_kernel", 2, 2.0 * T * top * ff * W * 2, "flops"),
             ("fast_kernel<128, 32, 4, false>", 2, 2.0 * T * top * ff * W * 2, "flops"),
             ("attn_prefill_mma", 1, 4.0 * H * D * keys, "flops"),
         ]),

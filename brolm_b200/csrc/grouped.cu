@@ -20,13 +20,13 @@ constexpr int GBM = 64, GBN = 64;
 // ---------------------------------------------------------------------------
 // Router: z = Wr x in float, the `top` largest z (ties: the lower index), weight
 // f(z) with f = logistic function.  A block takes RT tokens (one when there are
-// few, so that more SMs take part; four when there are many, so that a row of
-// Wr is fetched once for four tokens); a warp takes an expert at a time for all
+// few, so that more SMs take part, with 32 warps so that many experts' rows are in
+// flight at once; four when there are many, so that a row of Wr is fetched once for four tokens); a warp takes an expert at a time for all
 // of the block's tokens.  A (token, expert) sum is the lanes' strided partial
 // sums, added by one fixed tree: it does not depend on what else is in the block.
 // ---------------------------------------------------------------------------
 template <typename T, int RT>
-__global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ wr,
+__global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ wr,
                                                     int E, int D, int top, int tokens, int vec,
                                                     int32_t* __restrict__ ids, float* __restrict__ wts) {
     extern __shared__ float z[];                       // [RT][E]
@@ -132,14 +132,14 @@ __global__ void __launch_bounds__(256) route_kernel(const T* __restrict__ x, lon
 
 // ---------------------------------------------------------------------------
 // Grouping: pairs p = token * top + choice, each with an expert id -> the pairs in
-// expert order (perm), the experts' first rows (offsets) and the list of 64-row tiles.
+// expert order (perm), the experts' first rows (offsets) and the list of tiles of `tile_rows` rows.
 // One block; the order of an expert's pairs among themselves is not fixed, and no
 // result depends on it.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__ ids, int P, int E,
                                                      int32_t* __restrict__ perm, int32_t* __restrict__ offsets,
                                                      int32_t* __restrict__ tile_group, int32_t* __restrict__ tile_row0,
-                                                     int max_tiles) {
+                                                     int max_tiles, int tile_rows) {
     extern __shared__ int sh[];                        // counts [E], starts [E]
     int* counts = sh;
     int* starts = sh + E;
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(1024) group_kernel(const int32_t* __restrict__
         for (int e = 0; e < E; ++e) {
             starts[e] = row;
             offsets[e] = row;
-            for (int r = 0; r < counts[e] && tile < max_tiles; r += GBM) {
+            for (int r = 0; r < counts[e] && tile < max_tiles; r += tile_rows) {
                 tile_group[tile] = e;
                 tile_row0[tile] = row + r;
                 ++tile;
@@ -607,7 +607,7 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
     const size_t smem = (size_t)rt * experts * sizeof(float);
     const int blocks = (tokens + rt - 1) / rt;
 #define BROLM_ROUTE(T, RT)                                                                                        \
-    route_kernel<T, RT><<<blocks, 256, smem, stream>>>((const T*)x, ldx, (const T*)wr, experts, width, top, tokens, \
+    route_kernel<T, RT><<<blocks, RT == 1 ? 1024 : 256, smem, stream>>>((const T*)x, ldx, (const T*)wr, experts, width, top, tokens, \
                                                        vec, (int32_t*)ids, (float*)wts)
     if (dtype == BROLM_F32) {
         if (many) BROLM_ROUTE(float, 4); else BROLM_ROUTE(float, 1);
@@ -620,15 +620,17 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
     return launch_status();
 }
 
-// The tile list has room for max_tiles = ceil(pairs / 64) + experts entries.
+// The tile list has room for max_tiles = ceil(pairs / tile_rows) + experts entries; tile_rows is 64 for the
+// products of this file and 128 for the tcgen05 one.
 BROLM_API int brolm_group_pairs(const void* ids, int pairs, int experts, void* perm, void* offsets, void* tile_group,
-                                void* tile_row0, int max_tiles, cudaStream_t stream) {
+                                void* tile_row0, int max_tiles, int tile_rows, cudaStream_t stream) {
     if (pairs <= 0) return BROLM_OK;
+    if (tile_rows != GBM && tile_rows != 2 * GBM) return BROLM_ERR_BAD_SIZE;
     if (experts <= 0 || experts > 4096) return BROLM_ERR_TOO_LARGE;
     group_kernel<<<1, 1024, 2 * (size_t)experts * sizeof(int), stream>>>((const int32_t*)ids, pairs, experts,
                                                                         (int32_t*)perm, (int32_t*)offsets,
                                                                         (int32_t*)tile_group, (int32_t*)tile_row0,
-                                                                        max_tiles);
+                                                                        max_tiles, tile_rows);
     return launch_status();
 }
 

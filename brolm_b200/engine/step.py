@@ -220,7 +220,8 @@ class Engine:
         if self.device.type != "cuda" or self.model.dtype != torch.bfloat16:
             return
         codes = {"gemm_tc": kernels.gemm_tc_status(reset=True), "attn_tc": kernels.attention_tc_status(reset=True),
-                 "gemm_stream": kernels.gemm_stream_status(reset=True)}
+                 "gemm_stream": kernels.gemm_stream_status(reset=True),
+                 "grouped_tc": kernels.grouped_tc_status(reset=True)}
         bad = {k: v for k, v in codes.items() if v}
         if bad:
             raise StepError(f"{where}: a wait inside a tensor-core kernel ran out ({bad}), in this step or in a "

@@ -290,25 +290,87 @@ def route_topk(x: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tenso
 
 
 GROUP_ROWS = 64          # rows of a tile of the grouped product
+GROUP_ROWS_TC = 128      # ... of the tcgen05 grouped product
 
 
-def group_tiles(pairs: int, experts: int) -> int:
+def group_tiles(pairs: int, experts: int, rows: int = GROUP_ROWS) -> int:
     """Room the tile list of ``group_pairs`` needs: every expert may end with a tile that is not full."""
-    return (pairs + GROUP_ROWS - 1) // GROUP_ROWS + experts
+    return (pairs + rows - 1) // rows + experts
 
 
-def group_pairs(ids: torch.Tensor, experts: int, perm: torch.Tensor, offsets: torch.Tensor, tiles: torch.Tensor) -> None:
+def group_pairs(ids: torch.Tensor, experts: int, perm: torch.Tensor, offsets: torch.Tensor, tiles: torch.Tensor,
+                rows: int = GROUP_ROWS) -> None:
     """Sort the (token, choice) pairs of ``ids`` [tokens, top] by expert, on the device: ``perm`` [pairs] the
     pairs in expert order, ``offsets`` [experts + 1] each expert's first row, ``tiles`` [2, group_tiles]
-    (expert, first row) of every 64-row tile, expert -1 beyond the last."""
+    (expert, first row) of every tile of ``rows`` rows, expert -1 beyond the last."""
     pairs = ids.numel()
     for t in (ids, perm, offsets, tiles):
         assert t.dtype == torch.int32 and t.is_contiguous()
-    assert perm.numel() == pairs and offsets.numel() == experts + 1 and tiles.shape == (2, group_tiles(pairs, experts))
+    assert rows in (GROUP_ROWS, GROUP_ROWS_TC)
+    assert perm.numel() == pairs and offsets.numel() == experts + 1
+    assert tiles.shape == (2, group_tiles(pairs, experts, rows))
     f = _fn("grouped", "brolm_group_pairs", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                             c_void_p])
+                                             c_int, c_void_p])
     _check(f(_ptr(ids), pairs, experts, _ptr(perm), _ptr(offsets), _ptr(tiles[0]), _ptr(tiles[1]), tiles.shape[1],
-             _stream()), "group_pairs")
+             rows, _stream()), "group_pairs")
+
+
+# From how many pairs per expert on the experts' products run on tcgen05 (128-row tiles): below it most of
+# a tile would be rows that are dropped, and the mma.sync kernel with its 64-row tiles is ahead.
+EXPERTS_TC_ROWS = int(os.environ.get("BROLM_EXPERTS_TC_ROWS", "64"))
+
+
+def experts_tc_ok(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, pairs: int) -> bool:
+    """Whether the two products of routed experts over ``pairs`` (token, choice) pairs go to the tcgen05
+    grouped kernel: bfloat16 on the device, enough rows per expert, sizes a TMA box takes."""
+    E, F, W = w_up.shape
+    return (x.is_cuda and x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0
+            and x.stride(0) % 8 == 0 and pairs >= max(GROUP_ROWS_TC, EXPERTS_TC_ROWS * E))
+
+
+def gather_rows(x: torch.Tensor, perm: torch.Tensor, top: int, out: torch.Tensor) -> None:
+    """out[s, :] = x[perm[s] // top, :]: the tokens' rows in the order of their sorted pairs (bfloat16)."""
+    assert x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and x.stride(1) == 1 and out.is_contiguous()
+    assert perm.dtype == torch.int32 and out.shape == (perm.numel(), x.shape[1])
+    f = _fn("grouped_tc", "brolm_gather_rows", [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(perm), top, perm.numel(), x.shape[1], _ptr(out), _stream()), "gather_rows")
+
+
+def experts_linear_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, perm: torch.Tensor,
+                      offsets: torch.Tensor, tiles: torch.Tensor, top: int, tokens: int,
+                      scale: Optional[torch.Tensor] = None, activation: str = "none", down: bool = False) -> None:
+    """``experts_linear`` on tcgen05, for rows already in expert order: a (pairs, K); ``tiles`` the list of
+    128-row tiles.  First product: out (pairs, N) = act(scale[pair] * (W[e] a[row])), the gate applied to the
+    float sums; second: out float32 [top, tokens, N]."""
+    E, N, K = weight.shape
+    pairs = perm.numel()
+    assert a.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+    assert a.stride(1) == 1 and out.is_contiguous() and a.shape == (pairs, K) and pairs == top * tokens
+    assert tiles.shape == (2, group_tiles(pairs, E, GROUP_ROWS_TC))
+    if down:
+        assert out.dtype == torch.float32 and tuple(out.shape) == (top, tokens, N)
+    else:
+        assert scale is not None and scale.dtype == torch.float32 and scale.numel() == pairs and scale.is_contiguous()
+        assert tuple(out.shape) == (pairs, N) and out.dtype in (torch.float32, torch.bfloat16)
+    if activation not in EXPERT_ACTS:
+        raise KernelError(f"experts_linear_tc: unknown activation '{activation}' (known: {sorted(EXPERT_ACTS)})")
+    f = _fn("grouped_tc", "brolm_experts_linear_tc", [c_int, c_void_p, c_long, c_long, c_void_p, c_int, c_void_p, c_long,
+                                                      c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                      c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(1 if down else 0, _ptr(a), a.stride(0), pairs, _ptr(weight), E, _ptr(out), N,
+             1 if out.dtype == torch.float32 else 0, EXPERT_ACTS[activation], N, K, _ptr(tiles[0]), _ptr(tiles[1]),
+             _ptr(offsets), _ptr(perm), _ptr(scale) if scale is not None else None, top, tokens, tiles.shape[1],
+             _stream()), "experts_linear_tc")
+
+
+def grouped_tc_status(reset: bool = False) -> int:
+    """0 if no bounded wait inside the tcgen05 grouped product ever ran out; otherwise its code.  Synchronises."""
+    if not library_loaded("grouped_tc"):
+        return 0
+    f = load_library("grouped_tc").brolm_grouped_tc_status
+    f.argtypes = [c_int]
+    f.restype = c_int
+    return f(1 if reset else 0)
 
 
 def heads_linear(a: torch.Tensor, a_head: int, weight: torch.Tensor, out: torch.Tensor, o_head: int) -> None:
@@ -587,7 +649,7 @@ def gemm_tc_status(reset: bool = False) -> int:
     return f(1 if reset else 0)
 
 
-WAIT_LIBRARIES = ("gemm_tc", "gemm_tc2", "gemm_stream", "attn_tc")
+WAIT_LIBRARIES = ("gemm_tc", "gemm_tc2", "gemm_stream", "attn_tc", "grouped_tc")
 
 
 def wait_control(library: str, cycles: int = 0, stall_code: int = 0) -> None:
@@ -872,7 +934,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale",
-           "embed_pairs", "concat_cast", "latent_rows", "route_topk", "group_tiles", "group_pairs", "heads_linear",
+           "embed_pairs", "concat_cast", "latent_rows", "route_topk", "group_tiles", "group_pairs", "experts_tc_ok", "gather_rows", "experts_linear_tc", "grouped_tc_status", "heads_linear",
            "experts_linear", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",

@@ -43,6 +43,7 @@ LIBRARIES: dict[str, list[str]] = {
     "sampling": ["sampling.cu"],
     "latent": ["latent.cu"],
     "grouped": ["grouped.cu"],
+    "grouped_tc": ["grouped_tc.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
 

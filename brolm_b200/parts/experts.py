@@ -15,8 +15,10 @@ class RoutedExperts(Part):
     element type), not its output.  ``activation``: "relu2" (the square of relu) or "none".
 
     On the device: route -> sort the (token, choice) pairs by expert -> one grouped product per matrix over
-    64-row tiles of each expert's pairs -> float results [top, tokens, hidden], which the residual kernel
-    adds in the order of the choices.  Nothing is read back to the host.
+    tiles of each expert's pairs -> float results [top, tokens, hidden], which the residual kernel
+    adds in the order of the choices.  Nothing is read back to the host.  With many pairs per expert (a
+    prompt) the products run on tcgen05 over 128-row tiles, the tokens' rows first copied into expert order;
+    with few (decoding) on mma.sync over 64-row tiles, as a stream of the chosen experts' matrices.
     """
 
     kind = "feedforward"
@@ -59,9 +61,20 @@ class RoutedExperts(Part):
         kernels.route_topk(x, self.router, self.top, ids, gates)
         perm = torch.empty(pairs, dtype=torch.int32, device=dev)
         offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
+        u = torch.empty((pairs, self.inter), dtype=x.dtype, device=dev)
+        if kernels.experts_tc_ok(x, self.w_up, self.w_down, pairs):
+            rows = kernels.GROUP_ROWS_TC
+            tiles = torch.empty((2, kernels.group_tiles(pairs, self.experts, rows)), dtype=torch.int32, device=dev)
+            kernels.group_pairs(ids, self.experts, perm, offsets, tiles, rows)
+            xs = torch.empty((pairs, self.hidden), dtype=x.dtype, device=dev)
+            kernels.gather_rows(x, perm, self.top, xs)
+            kernels.experts_linear_tc(xs, self.w_up, u, perm, offsets, tiles, self.top, T, scale=gates,
+                                      activation=self.activation)
+            y = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)
+            kernels.experts_linear_tc(u, self.w_down, y, perm, offsets, tiles, self.top, T, down=True)
+            return y
         tiles = torch.empty((2, kernels.group_tiles(pairs, self.experts)), dtype=torch.int32, device=dev)
         kernels.group_pairs(ids, self.experts, perm, offsets, tiles)
-        u = torch.empty((pairs, self.inter), dtype=x.dtype, device=dev)
         kernels.experts_linear(x, self.w_up, u, perm, offsets, tiles, self.top, T, scale=gates,
                                activation=self.activation)
         y = torch.empty((self.top, T, self.hidden), dtype=torch.float32, device=dev)

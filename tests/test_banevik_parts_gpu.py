@@ -93,10 +93,12 @@ def test_router(dtype, E, top, D):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,E,top,D,F", [(1, 4, 2, 32, 16), (7, 6, 1, 40, 24), (70, 3, 3, 48, 40), (300, 5, 2, 36, 20),
-                                         (3, 9, 1, 64, 72), (300, 4, 2, 64, 136), (5, 8, 2, 64, 72), (40, 2, 1, 128, 64)])
+                                         (3, 9, 1, 64, 72), (300, 4, 2, 64, 136), (5, 8, 2, 64, 72), (40, 2, 1, 128, 64),
+                                         (100, 4, 2, 64, 136), (700, 4, 2, 72, 264), (520, 2, 1, 320, 128)])
 def test_routed_experts_part(dtype, T, E, top, D, F):
     """Experts with many rows (several tiles), with one row, with none; sizes that are no multiples of 8 (the plain
-    kernel), aligned sizes with many rows (the pipelined kernel) and with a few (the streaming kernel)."""
+    kernel), aligned sizes with many rows per expert (the tcgen05 kernel, also with sizes that are no multiples of
+    its tiles), with fewer (the pipelined kernel) and with a few (the streaming kernel)."""
     part = RoutedExperts(D, F, E, top)
     g = torch.Generator().manual_seed(T)
     ws = {n: (torch.randn(s.shape, generator=g) * (1.0 if n == "router" else 0.25)).to(dtype)
@@ -119,6 +121,44 @@ def test_routed_experts_part(dtype, T, E, top, D, F):
     keep = [t for t in range(T) if margins[t] > (1e-5 if dtype == torch.float32 else 0.02)]
     assert len(keep) >= T * 0.7
     assert rel(got[keep], ref[keep]) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("counts", [[0, 1, 128, 129, 300, 0, 70], [256, 0, 0, 127], [5, 640]])
+@pytest.mark.parametrize("N,K", [(256, 64), (40, 200), (520, 72)])
+def test_grouped_products_on_tcgen05_with_uneven_experts(counts, N, K):
+    """The two products over hand-made expert loads: experts without rows, with one, with a full tile and one more,
+    with several tiles; outputs narrower and wider than a tile, a depth that is no multiple of a stage."""
+    E, top = len(counts), 2
+    g = torch.Generator().manual_seed(sum(counts) + N)
+    expert_of = torch.cat([torch.full((c,), e, dtype=torch.int32) for e, c in enumerate(counts)])
+    pairs = expert_of.numel() + (expert_of.numel() & 1)
+    ids = torch.full((pairs,), E - 1, dtype=torch.int32)
+    ids[torch.randperm(pairs, generator=g)[:expert_of.numel()]] = expert_of
+    tokens = pairs // top
+    ids = ids.view(tokens, top).to(DEV)
+    perm = torch.empty(pairs, dtype=torch.int32, device=DEV)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    tiles = torch.empty((2, kernels.group_tiles(pairs, E, kernels.GROUP_ROWS_TC)), dtype=torch.int32, device=DEV)
+    kernels.group_pairs(ids, E, perm, offsets, tiles, kernels.GROUP_ROWS_TC)
+    x = torch.randn(tokens, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=g) * 0.2).to(torch.bfloat16)
+    gates = torch.rand(tokens, top, generator=g) + 0.25
+    xs = torch.empty((pairs, K), dtype=torch.bfloat16, device=DEV)
+    kernels.gather_rows(x.to(DEV), perm, top, xs)
+    order = perm.cpu().long()
+    assert torch.equal(xs.cpu(), x[order // top])
+    assert torch.equal(ids.view(-1).cpu()[order], torch.sort(ids.view(-1).cpu()).values)
+    u = torch.empty((pairs, N), dtype=torch.bfloat16, device=DEV)
+    kernels.experts_linear_tc(xs, w.to(DEV), u, perm, offsets, tiles, top, tokens, scale=gates.to(DEV), activation="relu2")
+    y = torch.empty((top, tokens, N), dtype=torch.float32, device=DEV)
+    kernels.experts_linear_tc(xs, w.to(DEV), y, perm, offsets, tiles, top, tokens, down=True)
+    assert kernels.grouped_tc_status() == 0
+    flat_ids = ids.view(-1).cpu().long()
+    sums = torch.einsum("pk,pnk->pn", x.double()[torch.arange(pairs) // top], w.double()[flat_ids])      # by pair
+    ref_u = torch.relu(sums * gates.view(-1, 1).double()) ** 2
+    assert rel(u.cpu()[torch.argsort(order)], ref_u) < 8e-3
+    ref_y = sums.view(tokens, top, N).transpose(0, 1)
+    assert rel(y, ref_y) < 1e-5 + 1e-6 * K
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
