@@ -93,3 +93,31 @@ def test_a_step_whose_kernel_gave_up_raises_and_the_engine_goes_on():
     again = eng.step([s], [prompt])
     assert torch.equal(again, good)
     eng.close([s])
+
+
+def test_routed_experts_whose_wait_runs_out():
+    """The tcgen05 grouped product: the epilogue's wait for its accumulator never completes."""
+    from brolm_b200.parts import RoutedExperts
+    T, E, top, D, F = 600, 4, 2, 64, 128
+    part = RoutedExperts(D, F, E, top)
+    g = torch.Generator().manual_seed(5)
+    part.bind({n: (torch.randn(s.shape, generator=g) * 0.25).to(torch.bfloat16).to(DEV)
+               for n, s in part.param_specs().items()})
+    x = torch.randn(T, D, generator=g).to(torch.bfloat16).to(DEV)
+    assert kernels.experts_tc_ok(x, part.w_up, part.w_down, T * top)
+
+    def run():
+        y = part.forward(x, None)
+        torch.cuda.synchronize()
+        return y
+
+    good = run()
+    assert kernels.grouped_tc_status(reset=True) == 0
+    kernels.wait_control("grouped_tc", cycles=LIMIT, stall_code=3)
+    try:
+        run()
+        assert kernels.grouped_tc_status(reset=True) == 3 and kernels.grouped_tc_status() == 0
+    finally:
+        kernels.wait_control("grouped_tc", 0, 0)
+    again = run()
+    assert kernels.grouped_tc_status() == 0 and torch.equal(again, good)
