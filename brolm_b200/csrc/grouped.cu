@@ -21,10 +21,37 @@ constexpr int GBM = 64, GBN = 64;
 // Router: z = Wr x in float, the `top` largest z (ties: the lower index), weight
 // f(z) with f = logistic function.  A block takes RT tokens (one when there are
 // few, so that more SMs take part, with 32 warps so that many experts' rows are in
-// flight at once; four when there are many, so that a row of Wr is fetched once for four tokens); a warp takes an expert at a time for all
-// of the block's tokens.  A (token, expert) sum is the lanes' strided partial
+// flight at once; four when there are many, so that a row of Wr is fetched once for
+// four tokens); a warp takes an expert at a time for all of the block's tokens.  A (token, expert) sum is the lanes' strided partial
 // sums, added by one fixed tree: it does not depend on what else is in the block.
 // ---------------------------------------------------------------------------
+// A warp picks for token t from its scores zr [E] in shared memory (which it overwrites): the `top` largest,
+// ties to the lower index, best first.
+__device__ __forceinline__ void pick_top(float* zr, int E, int top, int t, int lane, int32_t* __restrict__ ids,
+                                         float* __restrict__ wts) {
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = zr[e];
+            if (v > best || (v == best && e < at)) { best = v; at = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at >= E) at = 0;                       // (every score was -inf or NaN)
+        if (lane == 0) {
+            ids[(size_t)t * top + k] = at;
+            wts[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
+            zr[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+}
+
 template <typename T, int RT>
 __global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ wr,
                                                     int E, int D, int top, int tokens, int vec,
@@ -103,31 +130,21 @@ __global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __
         }
     }
     __syncthreads();
-    for (int r = warp; r < nt; r += nwarps) {          // a warp picks for a token
-        float* zr = z + r * E;
-        const int t = t0 + r;
-        for (int k = 0; k < top; ++k) {
-            float best = -INFINITY;
-            int at = 0x7fffffff;
-            for (int e = lane; e < E; e += 32) {
-                const float v = zr[e];
-                if (v > best || (v == best && e < at)) { best = v; at = e; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
-            }
-            if (at >= E) at = 0;                       // (every score was -inf or NaN)
-            if (lane == 0) {
-                ids[(size_t)t * top + k] = at;
-                wts[(size_t)t * top + k] = 1.0f / (1.0f + expf(-best));
-                zr[at] = -INFINITY;
-            }
-            __syncwarp();
-        }
-    }
+    for (int r = warp; r < nt; r += nwarps) pick_top(z + r * E, E, top, t0 + r, lane, ids, wts);
+}
+
+// The choice alone, for scores that a matrix product left in memory: z [tokens, E] float (ldz between rows).
+// A block takes eight tokens, a warp one.
+__global__ void __launch_bounds__(256) route_pick_kernel(const float* __restrict__ zs, long ldz, int E, int top, int tokens,
+                                                         int32_t* __restrict__ ids, float* __restrict__ wts) {
+    extern __shared__ float z[];                       // [8][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= tokens) return;
+    float* zr = z + warp * E;
+    for (int e = lane; e < E; e += 32) zr[e] = zs[(size_t)t * ldz + e];
+    __syncwarp();
+    pick_top(zr, E, top, t, lane, ids, wts);
 }
 
 // ---------------------------------------------------------------------------
@@ -617,6 +634,17 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
         return BROLM_ERR_BAD_DTYPE;
     }
 #undef BROLM_ROUTE
+    return launch_status();
+}
+
+// The same choice from scores already in memory: z [tokens, experts] float, ldz floats between rows.
+BROLM_API int brolm_route_pick(const void* z, long ldz, int tokens, int experts, int top, void* ids, void* wts,
+                               cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (experts <= 0 || top <= 0 || top > experts) return BROLM_ERR_BAD_SIZE;
+    if (experts > 1024) return BROLM_ERR_TOO_LARGE;          // (eight rows of scores in the default shared memory)
+    route_pick_kernel<<<(tokens + 7) / 8, 256, (size_t)8 * experts * sizeof(float), stream>>>(
+        (const float*)z, ldz, experts, top, tokens, (int32_t*)ids, (float*)wts);
     return launch_status();
 }
 

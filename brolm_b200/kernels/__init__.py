@@ -289,6 +289,15 @@ def route_topk(x: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tenso
              _ptr(weights), _stream()), "route_topk")
 
 
+def route_pick(z: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """The choice of ``route_topk`` from scores z [tokens, experts] float32 that a matrix product left in memory."""
+    assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1 and z.shape[1] <= 1024
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
+    assert ids.shape == (z.shape[0], top) and weights.shape == ids.shape
+    f = _fn("grouped", "brolm_route_pick", [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(z), z.stride(0), z.shape[0], z.shape[1], top, _ptr(ids), _ptr(weights), _stream()), "route_pick")
+
+
 GROUP_ROWS = 64          # rows of a tile of the grouped product
 GROUP_ROWS_TC = 128      # ... of the tcgen05 grouped product
 
@@ -934,7 +943,7 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, s
 
 
 __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "device_sms", "wait_control", "embed_scale",
-           "embed_pairs", "concat_cast", "latent_rows", "route_topk", "group_tiles", "group_pairs", "experts_tc_ok", "gather_rows", "experts_linear_tc", "grouped_tc_status", "heads_linear",
+           "embed_pairs", "concat_cast", "latent_rows", "route_topk", "route_pick", "group_tiles", "group_pairs", "experts_tc_ok", "gather_rows", "experts_linear_tc", "grouped_tc_status", "heads_linear",
            "experts_linear", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",

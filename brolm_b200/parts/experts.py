@@ -5,12 +5,14 @@ import torch
 
 from .. import kernels
 from .base import ParamSpec, Part, register_part
+from .linear import linear
 
 
 class RoutedExperts(Part):
     """y = sum over the token's ``top`` experts e of  W_down[e] act(W_up[e] (g_e x)),  no biases.
 
-    Router: z = W_r x summed in float; the ``top`` largest z are chosen; g_e = logistic(z_e), not
+    Router: z = W_r x summed in float (by the router kernel in one fixed order; for a prompt in bfloat16 by a
+    matrix product with float accumulation); the ``top`` largest z are chosen; g_e = logistic(z_e), not
     renormalised.  With ``scale_input`` the gate multiplies the expert's input (one rounding to the step's
     element type), not its output.  ``activation``: "relu2" (the square of relu) or "none".
 
@@ -23,6 +25,7 @@ class RoutedExperts(Part):
 
     kind = "feedforward"
     graph_safe = True
+    ROUTER_PRODUCT_ROWS = 256      # from this many tokens on the router's scores are a matrix product
 
     def __init__(self, hidden: int, inter: int, experts: int, top: int, activation: str = "relu2",
                  scale_input: bool = True):
@@ -58,7 +61,12 @@ class RoutedExperts(Part):
         pairs = T * self.top
         ids = torch.empty((T, self.top), dtype=torch.int32, device=dev)
         gates = torch.empty((T, self.top), dtype=torch.float32, device=dev)
-        kernels.route_topk(x, self.router, self.top, ids, gates)
+        if x.dtype == torch.bfloat16 and T >= self.ROUTER_PRODUCT_ROWS and self.experts <= 1024 and self.hidden % 8 == 0:
+            # a prompt: the scores as one matrix product (bfloat16 products are exact in float, the sums are
+            # float), then the choice; the router kernel's float multiply-adds are what bounds it from here on
+            kernels.route_pick(linear(x, self.router, out_dtype=torch.float32), self.top, ids, gates)
+        else:
+            kernels.route_topk(x, self.router, self.top, ids, gates)
         perm = torch.empty(pairs, dtype=torch.int32, device=dev)
         offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
         u = torch.empty((pairs, self.inter), dtype=x.dtype, device=dev)

@@ -89,6 +89,12 @@ def test_router(dtype, E, top, D):
     ref = torch.topk(z, top, dim=1)
     assert torch.equal(ids.cpu().long(), ref.indices)                  # (the operands are the same numbers: no close calls)
     assert rel(wts, torch.sigmoid(ref.values)) < 1e-5
+    # the choice alone, from scores in memory (rows further apart than E)
+    held = torch.zeros((70, E + 3), dtype=torch.float32, device=DEV)
+    held[:, :E] = z.float().to(DEV)
+    ids2, wts2 = torch.empty_like(ids), torch.empty_like(wts)
+    kernels.route_pick(held[:, :E], top, ids2, wts2)
+    assert torch.equal(ids2.cpu().long(), ref.indices) and rel(wts2, torch.sigmoid(ref.values)) < 1e-5
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
