@@ -129,7 +129,7 @@ def test_routed_experts_part(dtype, T, E, top, D, F):
     assert rel(got[keep], ref[keep]) <= TOL[dtype]
 
 
-@pytest.mark.parametrize("counts", [[0, 1, 128, 129, 300, 0, 70], [256, 0, 0, 127], [5, 640]])
+@pytest.mark.parametrize("counts", [[0, 1, 128, 129, 300, 0, 70], [256, 0, 0, 127], [5, 600], [257, 15, 16, 17, 255]])
 @pytest.mark.parametrize("N,K", [(256, 64), (40, 200), (520, 72)])
 def test_grouped_products_on_tcgen05_with_uneven_experts(counts, N, K):
     """The two products over hand-made expert loads: experts without rows, with one, with a full tile and one more,
