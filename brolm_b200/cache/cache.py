@@ -12,7 +12,16 @@ Layers whose needs are equal form a *group* with storage of its own:
 * a state group holds one tensor of fixed shape per (layer, slot), zeroed when
   the slot is taken;
 * a group without values keeps one row per token that is key and value at once
-  (latent attention), in the keys' store alone.
+  (latent attention), in the keys' store alone;
+* a group whose values have a size of their own (``v_dim``) keeps them in a store
+  of that row size;
+* a group that sees a chunk of C keys (position p sees the keys from
+  ``p - p % C`` on) holds the same ring as a window of C: a chunk never spans
+  more places than the ring has.
+
+A schedule entry may keep several things at once (a mixer made of two: keys
+and values for one, a state for the other): its spec is then a tuple of specs
+and its entry a ``CacheEntries`` with one ``CacheEntry`` per spec, in order.
 
 Storage of a key/value group is ``[layer][page][kv_head][page_size][head_dim]``
 for keys and the same for values; all layers of a group share the page ids, so
@@ -44,6 +53,8 @@ class KVSpec:
     head_dim: int
     window: Optional[int] = None
     values: bool = True
+    v_dim: Optional[int] = None      # size of a value row when it is not head_dim
+    chunk: Optional[int] = None      # position p sees keys p - p % chunk .. p: kept like a window of that many
 
 
 @dataclasses.dataclass(frozen=True)
@@ -60,16 +71,25 @@ def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
+def kept_span(spec: KVSpec) -> Optional[int]:
+    """How many of the newest keys a sequence has to keep (None: all of them)."""
+    spans = [s for s in (spec.window, spec.chunk) if s]
+    return min(spans) if spans else None
+
+
 class KVGroup:
     def __init__(self, spec: KVSpec, entries: list[int], num_pages: int, page_size: int, dtype, device):
         self.spec = spec
         self.entries = entries
         self.page_size = page_size
-        self.ring = _round_up(spec.window, page_size) if spec.window else None
+        self.ring = _round_up(kept_span(spec), page_size) if kept_span(spec) else None
         self.pool = PagePool(num_pages)
         shape = (len(entries), num_pages, spec.n_kv, page_size, spec.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if spec.values else self.k
+        if not spec.values:
+            self.v = self.k
+        else:
+            self.v = torch.zeros(shape[:-1] + (spec.v_dim or spec.head_dim,), dtype=dtype, device=device)
         self.pages: dict[int, list[int]] = {}     # slot -> page ids in ring/position order
 
     @property
@@ -112,6 +132,12 @@ class CacheEntry:
         return self.group.data[self.index]
 
 
+@dataclasses.dataclass
+class CacheEntries:
+    """What a schedule entry with a tuple of specs keeps: one ``CacheEntry`` per spec, in the tuple's order."""
+    parts: list
+
+
 class Cache:
     """Slots, page pools and storage for the cache needs of a schedule.
 
@@ -146,27 +172,35 @@ class Cache:
         self.last_token = torch.zeros(self.max_slots + 1, dtype=torch.int32, device=self.device) \
             if keep_last_token else None
 
-        by_spec: dict[CacheSpec, list[int]] = {}
+        # (schedule entry, place in its tuple or None) of everything that is kept, by spec
+        by_spec: dict[CacheSpec, list[tuple]] = {}
         for i, s in enumerate(specs):
-            if s is not None:
-                by_spec.setdefault(s, []).append(i)
+            if isinstance(s, (tuple, list)):
+                self.entries[i] = CacheEntries([None] * len(s))
+                for k, sub in enumerate(s):
+                    by_spec.setdefault(sub, []).append((i, k))
+            elif s is not None:
+                by_spec.setdefault(s, []).append((i, None))
         for spec, idxs in by_spec.items():
             if isinstance(spec, KVSpec):
                 pages = self.num_pages
-                if spec.window:
-                    ring_pages = _round_up(spec.window, page_size) // page_size
+                if kept_span(spec):
+                    ring_pages = _round_up(kept_span(spec), page_size) // page_size
                     pages = min(pages, self.max_slots * ring_pages)
-                g = KVGroup(spec, idxs, pages, page_size, dtype, self.device)
+                g = KVGroup(spec, [i for i, _ in idxs], pages, page_size, dtype, self.device)
                 gid = len(self.kv_groups)
                 self.kv_groups.append(g)
             elif isinstance(spec, StateSpec):
-                g = StateGroup(spec, idxs, self.max_slots, dtype, self.device)
+                g = StateGroup(spec, [i for i, _ in idxs], self.max_slots, dtype, self.device)
                 gid = len(self.state_groups)
                 self.state_groups.append(g)
             else:
                 raise CacheError(f"unknown cache spec {spec!r}")
-            for j, i in enumerate(idxs):
-                self.entries[i] = CacheEntry(g, gid, j)
+            for j, (i, k) in enumerate(idxs):
+                if k is None:
+                    self.entries[i] = CacheEntry(g, gid, j)
+                else:
+                    self.entries[i].parts[k] = CacheEntry(g, gid, j)
 
     # slots ----------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -292,7 +326,7 @@ class Cache:
     def bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += g.k.numel() * g.k.element_size() * (2 if g.spec.values else 1)
+            n += g.k.numel() * g.k.element_size() + (g.v.numel() * g.v.element_size() if g.spec.values else 0)
         for g in self.state_groups:
             n += g.data.numel() * g.data.element_size()
         return n

@@ -21,6 +21,9 @@
 // query at position p iff 0 <= p - j < window (window <= 0: no window).
 // With a sink, a learned number per query head, the softmax's denominator also
 // holds exp(sink): a key that is always visible, is not scaled and has no value.
+// With a chunk size C (chunk > 0) a key must also lie in the query's own chunk: j >= p - p % C, chunks
+// counted from position 0 of the sequence.  Value rows may have a size of their own (vd), apart from
+// the size of query and key rows (hd).
 #include "common.cuh"
 
 namespace {
@@ -39,27 +42,30 @@ struct AttnArgs {
     // packed source
     const void* k;            // [tokens, kv_stride]; kv head g at g*hd
     const void* v;
-    int kv_stride;
+    int kv_stride;            // of k
+    int v_stride;             // of v
     // paged source
     const void* k_pages;      // [page][n_kv][page_size][hd]
     const void* v_pages;
     const int32_t* page_table;
     int pt_stride, ring, page_size;
     int n_kv, group, hd;
+    int vd;                   // size of a value row (and of an output row)
     float scale, cap;
     int window;
+    int chunk;                // > 0: keys before the start of the query's chunk are not visible
     const float* sink;        // [n_kv * group] or null: exp(sink[head]) joins the softmax's denominator, with no value
 };
 
-// DPL: output dims per lane = ceil(hd / 32) rounded up to the instantiated size.
+// DPL: output dims per lane = ceil(vd / 32) rounded up to the instantiated size.
 template <typename T, int DPL, bool PAGED>
 __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
     extern __shared__ __align__(16) float smem[];
-    const int hd = a.hd;
+    const int hd = a.hd, vd = a.vd;
     const int qs = hd + 4;                 // padded stride of q and k rows (floats)
     float* Qs = smem;                      // [ROWS][qs]
     float* Ks = Qs + ROWS * qs;            // [KT][qs]
-    float* Vs = Ks + KT * qs;              // [KT][hd]
+    float* Vs = Ks + KT * qs;              // [KT][vd]
 
     const int b = blockIdx.z, g = blockIdx.y;
     const int q0 = a.cu_q[b], q_len = a.cu_q[b + 1] - q0;
@@ -88,7 +94,9 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
     // key range of the whole tile
     const int tok_lo = row0 / a.group, tok_hi = (row0 + rows_here - 1) / a.group;
     const int pos_lo = first_pos + tok_lo, pos_hi = first_pos + tok_hi;
-    const int key_lo = max(0, pos_lo - window + 1), key_hi = pos_hi;   // inclusive
+    int key_lo = max(0, pos_lo - window + 1);
+    if (a.chunk > 0) key_lo = max(key_lo, pos_lo - pos_lo % a.chunk);
+    const int key_hi = pos_hi;   // inclusive
 
     // per-row state of this warp
     int rpos[RPW];
@@ -109,25 +117,36 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
         for (int idx = threadIdx.x; idx < KT * (hd / 8); idx += blockDim.x) {
             const int j = idx / (hd / 8), c = (idx - j * (hd / 8)) * 8;
             const int kp = t0 + j;
-            float kv[8] = {0, 0, 0, 0, 0, 0, 0, 0}, vv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            float kv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             if (kp >= key_lo && kp <= key_hi) {
                 if (PAGED) {
                     const int ridx = kp % a.ring;
                     const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
                     const size_t off = (((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * hd + c;
                     load8((const T*)a.k_pages + off, kv);
-                    load8((const T*)a.v_pages + off, vv);
                 } else {
-                    const size_t off = (size_t)(q0 + kp) * a.kv_stride + g * hd + c;
-                    load8((const T*)a.k + off, kv);
-                    load8((const T*)a.v + off, vv);
+                    load8((const T*)a.k + (size_t)(q0 + kp) * a.kv_stride + g * hd + c, kv);
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                Ks[j * qs + c + i] = kv[i];
-                Vs[j * hd + c + i] = vv[i];
+            for (int i = 0; i < 8; ++i) Ks[j * qs + c + i] = kv[i];
+        }
+        for (int idx = threadIdx.x; idx < KT * (vd / 8); idx += blockDim.x) {
+            const int j = idx / (vd / 8), c = (idx - j * (vd / 8)) * 8;
+            const int kp = t0 + j;
+            float vv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (kp >= key_lo && kp <= key_hi) {
+                if (PAGED) {
+                    const int ridx = kp % a.ring;
+                    const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
+                    const size_t off = (((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * vd + c;
+                    load8((const T*)a.v_pages + off, vv);
+                } else {
+                    load8((const T*)a.v + (size_t)(q0 + kp) * a.v_stride + g * vd + c, vv);
+                }
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) Vs[j * vd + c + i] = vv[i];
         }
         __syncthreads();
 
@@ -151,7 +170,8 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
         float p[RPW];
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
-            const bool visible = rpos[i] >= 0 && kp <= rpos[i] && rpos[i] - kp < window;
+            const bool visible = rpos[i] >= 0 && kp <= rpos[i] && rpos[i] - kp < window &&
+                                 (a.chunk <= 0 || kp >= rpos[i] - rpos[i] % a.chunk);
             const float sc = visible ? soft_cap(s[i] * a.scale, a.cap) : -INFINITY;
             const float tile_max = warp_max(sc);
             const float m_new = fmaxf(m[i], tile_max);
@@ -172,7 +192,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
 #pragma unroll
             for (int d = 0; d < DPL; ++d) {
                 const int dim = lane + 32 * d;
-                vj[d] = dim < hd ? Vs[j * hd + dim] : 0.0f;
+                vj[d] = dim < vd ? Vs[j * vd + dim] : 0.0f;
             }
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
@@ -192,18 +212,18 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
         float den = l[i];
         if (a.sink && m[i] > -INFINITY) den += expf(a.sink[head] - m[i]);
         const float inv = den > 0.0f ? 1.0f / den : 0.0f;
-        T* dst = og + (size_t)(q0 + tok) * a.out_stride + head * hd;
+        T* dst = og + (size_t)(q0 + tok) * a.out_stride + head * vd;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) {
             const int dim = lane + 32 * d;
-            if (dim < hd) dst[dim] = from_float<T>(acc[i][d] * inv);
+            if (dim < vd) dst[dim] = from_float<T>(acc[i][d] * inv);
         }
     }
 }
 
 template <typename T, int DPL>
 int launch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream_t stream) {
-    const size_t smem = (size_t)((ROWS + KT) * (a.hd + 4) + KT * a.hd) * sizeof(float);
+    const size_t smem = (size_t)((ROWS + KT) * (a.hd + 4) + KT * a.vd) * sizeof(float);
     if (smem > 227 * 1024) return BROLM_ERR_TOO_LARGE;
     dim3 grid((max_q_len * a.group + ROWS - 1) / ROWS, a.n_kv, batch);
     static size_t allowed[2] = {0, 0};        // raised once per size, not at every launch
@@ -224,7 +244,7 @@ int launch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream_t
 
 template <typename T>
 int dispatch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream_t stream) {
-    const int dpl = (a.hd + 31) / 32;
+    const int dpl = (a.vd + 31) / 32;
     if (dpl <= 1) return launch<T, 1>(a, paged, batch, max_q_len, stream);
     if (dpl <= 2) return launch<T, 2>(a, paged, batch, max_q_len, stream);
     if (dpl <= 4) return launch<T, 4>(a, paged, batch, max_q_len, stream);
@@ -242,21 +262,22 @@ BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out,
                               const void* kv_len, const void* k, const void* v, int kv_stride, const void* k_pages,
                               const void* v_pages, const void* page_table, int pt_stride, int ring, int page_size,
                               int n_kv, int group, int hd, float scale, float cap, int window, const void* sink,
-                              int batch, int max_q_len, cudaStream_t stream) {
+                              int batch, int max_q_len, int vd, int v_stride, int chunk, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     if (hd <= 0 || hd % 8 != 0 || hd > 512 || group <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
+    if (vd <= 0 || vd % 8 != 0 || vd > 512) return BROLM_ERR_BAD_SIZE;
     if (q_stride % 8 != 0 || out_stride % 8 != 0) return BROLM_ERR_ALIGNMENT;
     if (batch > 65535 || n_kv > 65535) return BROLM_ERR_TOO_LARGE;
     const bool paged = k_pages != nullptr;
     if (paged) {
         if (ring <= 0 || page_size <= 0 || page_size % KT != 0 || ring % page_size != 0) return BROLM_ERR_BAD_SIZE;
     } else {
-        if (!k || !v || kv_stride % 8 != 0) return BROLM_ERR_ALIGNMENT;
+        if (!k || !v || kv_stride % 8 != 0 || v_stride % 8 != 0) return BROLM_ERR_ALIGNMENT;
     }
     AttnArgs a;
     a.q = q; a.out = out; a.q_stride = q_stride; a.out_stride = out_stride;
     a.cu_q = (const int32_t*)cu_q; a.kv_len = (const int32_t*)kv_len;
-    a.k = k; a.v = v; a.kv_stride = kv_stride;
+    a.k = k; a.v = v; a.kv_stride = kv_stride; a.v_stride = v_stride; a.vd = vd; a.chunk = chunk;
     a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = (const int32_t*)page_table;
     a.pt_stride = pt_stride; a.ring = ring; a.page_size = page_size;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.sink = (const float*)sink;

@@ -27,8 +27,58 @@ constexpr int GBM = 64, GBN = 64;
 // ---------------------------------------------------------------------------
 // A warp picks for token t from its scores zr [E] in shared memory (which it overwrites): the `top` largest,
 // ties to the lower index, best first.
+// mode ROUTE_LOGISTIC: the weight of a chosen expert is the logistic function of its score.
+// mode ROUTE_SOFTMAX: s = softmax(z) over all experts; the choice goes by s + corr (a learned number per expert
+// that takes no part in the weights); the weights are the chosen s over their sum (+ 1e-20).
+enum : int { ROUTE_LOGISTIC = 0, ROUTE_SOFTMAX = 1 };
+
 __device__ __forceinline__ void pick_top(float* zr, int E, int top, int t, int lane, int32_t* __restrict__ ids,
-                                         float* __restrict__ wts) {
+                                         float* __restrict__ wts, int mode, const float* __restrict__ corr) {
+    if (mode == ROUTE_SOFTMAX) {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+        m = warp_max(m);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(zr[e] - m);
+            zr[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) zr[e] *= inv;
+        __syncwarp();
+        float total = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                const float sc = zr[e];                  // a chosen expert's place holds -inf
+                const float v = sc + (corr ? corr[e] : 0.0f);
+                if (v > best || (v == best && e < at)) { best = v; at = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (at >= E) at = 0;
+            if (lane == 0) {
+                const float w = zr[at] > -INFINITY ? zr[at] : 0.0f;
+                ids[(size_t)t * top + k] = at;
+                wts[(size_t)t * top + k] = w;
+                total += w;
+                zr[at] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            const float inv_total = 1.0f / (total + 1e-20f);
+            for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= inv_total;
+        }
+        return;
+    }
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int at = 0x7fffffff;
@@ -55,7 +105,8 @@ __device__ __forceinline__ void pick_top(float* zr, int E, int top, int t, int l
 template <typename T, int RT>
 __global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __restrict__ x, long ldx, const T* __restrict__ wr,
                                                     int E, int D, int top, int tokens, int vec,
-                                                    int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                                    int32_t* __restrict__ ids, float* __restrict__ wts, int mode,
+                                                    const float* __restrict__ corr) {
     extern __shared__ float z[];                       // [RT][E]
     const int t0 = blockIdx.x * RT;
     const int nt = min(RT, tokens - t0);
@@ -130,13 +181,14 @@ __global__ void __launch_bounds__(RT == 1 ? 1024 : 256) route_kernel(const T* __
         }
     }
     __syncthreads();
-    for (int r = warp; r < nt; r += nwarps) pick_top(z + r * E, E, top, t0 + r, lane, ids, wts);
+    for (int r = warp; r < nt; r += nwarps) pick_top(z + r * E, E, top, t0 + r, lane, ids, wts, mode, corr);
 }
 
 // The choice alone, for scores that a matrix product left in memory: z [tokens, E] float (ldz between rows).
 // A block takes eight tokens, a warp one.
 __global__ void __launch_bounds__(256) route_pick_kernel(const float* __restrict__ zs, long ldz, int E, int top, int tokens,
-                                                         int32_t* __restrict__ ids, float* __restrict__ wts) {
+                                                         int32_t* __restrict__ ids, float* __restrict__ wts, int mode,
+                                                         const float* __restrict__ corr) {
     extern __shared__ float z[];                       // [8][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * 8 + warp;
@@ -144,7 +196,7 @@ __global__ void __launch_bounds__(256) route_pick_kernel(const float* __restrict
     float* zr = z + warp * E;
     for (int e = lane; e < E; e += 32) zr[e] = zs[(size_t)t * ldz + e];
     __syncwarp();
-    pick_top(zr, E, top, t, lane, ids, wts);
+    pick_top(zr, E, top, t, lane, ids, wts, mode, corr);
 }
 
 // ---------------------------------------------------------------------------
@@ -248,7 +300,7 @@ __device__ __forceinline__ int tile_rows(const GroupedArgs& g, int bt, RowInfo* 
                 const int tok = p / g.top, choice = p - tok * g.top;
                 if (g.mode == MODE_UP) {
                     ri.a_off = (long)tok * g.lda;
-                    ri.scale = g.scale[p];
+                    ri.scale = g.scale ? g.scale[p] : 1.0f;
                     ri.o_off = (long)s * g.ldo;
                 } else {
                     ri.a_off = (long)s * g.lda;
@@ -613,8 +665,10 @@ int launch_grouped(int dtype, GroupedArgs& g, int row_tiles, bool few, cudaStrea
 }  // namespace
 
 // ids [tokens, top] int32 and wts [tokens, top] float: the chosen experts of every token, best first.
+// mode 0: the weights are the logistic function of the chosen scores; mode 1: softmax over all experts, the choice
+// by softmax + corr (float [experts] or null), the weights the chosen softmax values over their sum.
 BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* wr, int tokens, int experts, int width,
-                               int top, void* ids, void* wts, cudaStream_t stream) {
+                               int top, void* ids, void* wts, int mode, const void* corr, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (experts <= 0 || top <= 0 || top > experts || width <= 0) return BROLM_ERR_BAD_SIZE;
     if (experts > 8192) return BROLM_ERR_TOO_LARGE;
@@ -625,7 +679,7 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
     const int blocks = (tokens + rt - 1) / rt;
 #define BROLM_ROUTE(T, RT)                                                                                        \
     route_kernel<T, RT><<<blocks, RT == 1 ? 1024 : 256, smem, stream>>>((const T*)x, ldx, (const T*)wr, experts, width, top, tokens, \
-                                                       vec, (int32_t*)ids, (float*)wts)
+                                                       vec, (int32_t*)ids, (float*)wts, mode, (const float*)corr)
     if (dtype == BROLM_F32) {
         if (many) BROLM_ROUTE(float, 4); else BROLM_ROUTE(float, 1);
     } else if (dtype == BROLM_BF16) {
@@ -639,12 +693,12 @@ BROLM_API int brolm_route_topk(int dtype, const void* x, long ldx, const void* w
 
 // The same choice from scores already in memory: z [tokens, experts] float, ldz floats between rows.
 BROLM_API int brolm_route_pick(const void* z, long ldz, int tokens, int experts, int top, void* ids, void* wts,
-                               cudaStream_t stream) {
+                               int mode, const void* corr, cudaStream_t stream) {
     if (tokens <= 0) return BROLM_OK;
     if (experts <= 0 || top <= 0 || top > experts) return BROLM_ERR_BAD_SIZE;
     if (experts > 1024) return BROLM_ERR_TOO_LARGE;          // (eight rows of scores in the default shared memory)
     route_pick_kernel<<<(tokens + 7) / 8, 256, (size_t)8 * experts * sizeof(float), stream>>>(
-        (const float*)z, ldz, experts, top, tokens, (int32_t*)ids, (float*)wts);
+        (const float*)z, ldz, experts, top, tokens, (int32_t*)ids, (float*)wts, mode, (const float*)corr);
     return launch_status();
 }
 

@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(THREADS, 1) grouped_tc_kernel(const __grid_con
                     const int tok = p / g.top, choice = p - tok * g.top;
                     o_off = ((long)choice * g.tokens + tok) * g.ldo;
                 } else {
-                    gate = g.scale[p];
+                    gate = g.scale ? g.scale[p] : 1.0f;
                     o_off = (long)row * g.ldo;
                 }
             }

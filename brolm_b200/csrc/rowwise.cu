@@ -1,0 +1,284 @@
+// Row-wise steps between the matrix products of a layer, all with float arithmetic:
+//
+//   cast            out = x in another element type
+//   bias_act        out = act(sum of the parts of y + bias)
+//   scaled_sum      out = sa * (sum of a's parts) + sb * (sum of b's parts)
+//   qkv_norm_write  RMS norm of the whole query row and of the whole key row of a token (one
+//                   statistic over all heads), and keys and values into the paged cache; the
+//                   value rows may have a size of their own
+//   gate_group_norm out = rmsnorm per group of (y * silu(z)) * gain
+//   experts_combine out = sum over a token's choices of weight * (expert's result | the token's own
+//                   row for an identity expert) + the shared expert's result
+//
+// Inputs are float or bfloat16, outputs as asked for.  One block per token (row); a row's result
+// depends on that row alone.
+#include "common.cuh"
+
+namespace {
+
+enum : int { RACT_NONE = 0, RACT_RELU2 = 1, RACT_GELU_TANH = 2, RACT_SILU = 3 };
+
+__device__ __forceinline__ float row_act(float v, int act) {
+    if (act == RACT_RELU2) {
+        v = fmaxf(v, 0.0f);
+        return v * v;
+    }
+    if (act == RACT_GELU_TANH) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    if (act == RACT_SILU) return v / (1.0f + expf(-v));
+    return v;
+}
+
+template <typename X, typename O>
+__global__ void __launch_bounds__(256) cast_kernel(const X* __restrict__ x, O* __restrict__ out, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i + 3 < n) {
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = to_float(x[i + e]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) out[i + e] = from_float<O>(v[e]);
+    } else {
+        for (long long j = i; j < n; ++j) out[j] = from_float<O>(to_float(x[j]));
+    }
+}
+
+template <typename Y, typename B, typename O>
+__global__ void __launch_bounds__(256) bias_act_kernel(const Y* __restrict__ y, int n_parts, long long part_stride, long ldy,
+                                                       const B* __restrict__ bias, int act, O* __restrict__ out, long ldo,
+                                                       int cols) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    const Y* yr = y + (size_t)r * ldy + c;
+    float v = to_float(yr[0]);
+    for (int s = 1; s < n_parts; ++s) v += to_float(yr[(size_t)s * part_stride]);
+    if (bias) v += to_float(bias[c]);
+    out[(size_t)r * ldo + c] = from_float<O>(row_act(v, act));
+}
+
+__global__ void __launch_bounds__(256) scaled_sum_kernel(const float* __restrict__ a, int a_parts, long long a_stride, float sa,
+                                                         const float* __restrict__ b, int b_parts, long long b_stride, float sb,
+                                                         float* __restrict__ out, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float va = a[i], vb = b[i];
+    for (int s = 1; s < a_parts; ++s) va += a[(size_t)s * a_stride + i];
+    for (int s = 1; s < b_parts; ++s) vb += b[(size_t)s * b_stride + i];
+    out[i] = sa * va + sb * vb;
+}
+
+// proj row t: [ q: q_cols | k: k_cols | v: v_cols ] (float or bfloat16).  out row t takes the same layout in O.
+// whole_norm: q <- q * rsqrt(mean(q^2) + eps) * wq over all q_cols at once, the same for k with wk.
+// The cache of this layer is k_pages [page][n_kv][page_size][k_cols / n_kv], v_pages [...][v_cols / n_kv].
+template <typename X, typename W, typename O>
+__global__ void __launch_bounds__(256) qkv_norm_write_kernel(const X* __restrict__ proj, long ldp, int q_cols, int k_cols, int v_cols,
+                                                             const W* __restrict__ wq, const W* __restrict__ wk, float eps,
+                                                             int whole_norm, const int32_t* __restrict__ positions,
+                                                             O* __restrict__ out, long ldo, O* __restrict__ k_pages,
+                                                             O* __restrict__ v_pages, const int32_t* __restrict__ cache_rows,
+                                                             int n_kv, int page_size) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    pdl_wait();
+    if (pos < 0) return;                               // a padding row
+    const X* pr = proj + (size_t)t * ldp;
+    O* orow = out + (size_t)t * ldo;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (whole_norm) {
+        float sq = 0.0f, sk = 0.0f;
+        for (int i = threadIdx.x; i < q_cols; i += blockDim.x) {
+            const float v = to_float(pr[i]);
+            sq += v * v;
+        }
+        for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
+            const float v = to_float(pr[q_cols + i]);
+            sk += v * v;
+        }
+        sq = block_sum(sq, scratch);
+        sk = block_sum(sk, scratch);
+        inv_q = rsqrtf(sq / (float)q_cols + eps);
+        inv_k = rsqrtf(sk / (float)k_cols + eps);
+    }
+    const int crow = k_pages ? cache_rows[t] : -1;
+    const int kd = k_cols / n_kv, vd = v_cols / n_kv;
+    const size_t page = crow >= 0 ? (size_t)(crow / page_size) : 0, place = crow >= 0 ? (size_t)(crow % page_size) : 0;
+    for (int i = threadIdx.x; i < q_cols; i += blockDim.x) {
+        float v = to_float(pr[i]);
+        if (whole_norm) v = v * inv_q * to_float(wq[i]);
+        orow[i] = from_float<O>(v);
+    }
+    for (int i = threadIdx.x; i < k_cols; i += blockDim.x) {
+        float v = to_float(pr[q_cols + i]);
+        if (whole_norm) v = v * inv_k * to_float(wk[i]);
+        const O o = from_float<O>(v);
+        orow[q_cols + i] = o;
+        if (crow >= 0) {
+            const int g = i / kd, d = i - g * kd;
+            k_pages[((page * n_kv + g) * page_size + place) * kd + d] = o;
+        }
+    }
+    for (int i = threadIdx.x; i < v_cols; i += blockDim.x) {
+        const O o = from_float<O>(to_float(pr[q_cols + k_cols + i]));
+        orow[q_cols + k_cols + i] = o;
+        if (crow >= 0) {
+            const int g = i / vd, d = i - g * vd;
+            v_pages[((page * n_kv + g) * page_size + place) * vd + d] = o;
+        }
+    }
+}
+
+// out[t, g*gs + i] = (y * silu(z))[.] * rsqrt(mean over the group + eps) * w[.]; one block per (group, token)
+template <typename Z, typename W, typename O>
+__global__ void __launch_bounds__(256) gate_group_norm_kernel(const float* __restrict__ y, long ldy, const Z* __restrict__ z, long ldz,
+                                                              const W* __restrict__ w, float eps, int group_size,
+                                                              O* __restrict__ out, long ldo) {
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x, g = blockIdx.y;
+    const float* yr = y + (size_t)t * ldy + (size_t)g * group_size;
+    const Z* zr = z + (size_t)t * ldz + (size_t)g * group_size;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < group_size; i += blockDim.x) {
+        const float zz = to_float(zr[i]);
+        const float v = yr[i] * (zz / (1.0f + expf(-zz)));
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)group_size + eps);
+    for (int i = threadIdx.x; i < group_size; i += blockDim.x) {
+        const float zz = to_float(zr[i]);
+        const float v = yr[i] * (zz / (1.0f + expf(-zz)));
+        out[(size_t)t * ldo + (size_t)g * group_size + i] = from_float<O>(v * inv * to_float(w[(size_t)g * group_size + i]));
+    }
+}
+
+// y [top][tokens][hidden] float (rows of choices that named an identity expert are never read), x the experts'
+// input, shared [parts][tokens][hidden] float or null.
+template <typename X>
+__global__ void __launch_bounds__(256) experts_combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ ids,
+                                                              const float* __restrict__ wts, int top, int n_real,
+                                                              const X* __restrict__ x, long ldx,
+                                                              const float* __restrict__ shared, int shared_parts,
+                                                              long long shared_stride, float* __restrict__ out, int tokens,
+                                                              int hidden) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= hidden) return;
+    float acc = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        const int e = ids[(size_t)t * top + k];
+        const float w = wts[(size_t)t * top + k];
+        const float v = e < n_real ? y[((size_t)k * tokens + t) * hidden + c] : to_float(x[(size_t)t * ldx + c]);
+        acc = fmaf(w, v, acc);
+    }
+    for (int s = 0; s < shared_parts; ++s) acc += shared[(size_t)s * shared_stride + (size_t)t * hidden + c];
+    out[(size_t)t * hidden + c] = acc;
+}
+
+}  // namespace
+
+BROLM_API int brolm_cast(const void* x, int x_dtype, void* out, int out_dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return BROLM_OK;
+    const unsigned blocks = (unsigned)((n + 1023) / 1024);
+#define BROLM_CAST(X, O) return launch_pdl(cast_kernel<X, O>, dim3(blocks), dim3(256), 0, stream, (const X*)x, (O*)out, n)
+    if (x_dtype == BROLM_F32 && out_dtype == BROLM_BF16) BROLM_CAST(float, bf16);
+    if (x_dtype == BROLM_F32 && out_dtype == BROLM_F32) BROLM_CAST(float, float);
+    if (x_dtype == BROLM_BF16 && out_dtype == BROLM_F32) BROLM_CAST(bf16, float);
+    if (x_dtype == BROLM_BF16 && out_dtype == BROLM_BF16) BROLM_CAST(bf16, bf16);
+#undef BROLM_CAST
+    return BROLM_ERR_BAD_DTYPE;
+}
+
+BROLM_API int brolm_bias_act(const void* y, int y_dtype, int n_parts, long long part_stride, long ldy, const void* bias,
+                             int bias_dtype, int act, void* out, int out_dtype, long ldo, int rows, int cols,
+                             cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return BROLM_OK;
+    if (act < 0 || act > 3 || n_parts < 1) return BROLM_ERR_BAD_SIZE;
+    dim3 grid(rows, (cols + 255) / 256);
+#define BROLM_BA(Y, B, O) return launch_pdl(bias_act_kernel<Y, B, O>, grid, dim3(256), 0, stream, (const Y*)y, n_parts, \
+                                            part_stride, ldy, (const B*)bias, act, (O*)out, ldo, cols)
+#define BROLM_BA2(Y, B)                                 \
+    do {                                                \
+        if (out_dtype == BROLM_F32) BROLM_BA(Y, B, float); \
+        if (out_dtype == BROLM_BF16) BROLM_BA(Y, B, bf16); \
+        return BROLM_ERR_BAD_DTYPE;                     \
+    } while (0)
+    if (y_dtype == BROLM_F32 && bias_dtype == BROLM_F32) BROLM_BA2(float, float);
+    if (y_dtype == BROLM_F32 && bias_dtype == BROLM_BF16) BROLM_BA2(float, bf16);
+    if (y_dtype == BROLM_BF16 && bias_dtype == BROLM_F32) BROLM_BA2(bf16, float);
+    if (y_dtype == BROLM_BF16 && bias_dtype == BROLM_BF16) BROLM_BA2(bf16, bf16);
+#undef BROLM_BA2
+#undef BROLM_BA
+    return BROLM_ERR_BAD_DTYPE;
+}
+
+BROLM_API int brolm_scaled_sum(const void* a, int a_parts, long long a_stride, float sa, const void* b, int b_parts,
+                               long long b_stride, float sb, void* out, long long n, cudaStream_t stream) {
+    if (n <= 0) return BROLM_OK;
+    if (a_parts < 1 || b_parts < 1) return BROLM_ERR_BAD_SIZE;
+    return launch_pdl(scaled_sum_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)a, a_parts,
+                      a_stride, sa, (const float*)b, b_parts, b_stride, sb, (float*)out, n);
+}
+
+BROLM_API int brolm_qkv_norm_write(const void* proj, int x_dtype, long ldp, int q_cols, int k_cols, int v_cols,
+                                   const void* wq, const void* wk, int w_dtype, float eps, int whole_norm,
+                                   const void* positions, void* out, int out_dtype, long ldo, void* k_pages, void* v_pages,
+                                   const void* cache_rows, int n_kv, int page_size, int tokens, cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (n_kv <= 0 || k_cols % n_kv || v_cols % n_kv || q_cols <= 0) return BROLM_ERR_BAD_SIZE;
+    if (whole_norm && (!wq || !wk)) return BROLM_ERR_BAD_SIZE;
+#define BROLM_QN(X, W, O) return launch_pdl(qkv_norm_write_kernel<X, W, O>, dim3(tokens), dim3(256), 0, stream, (const X*)proj, \
+        ldp, q_cols, k_cols, v_cols, (const W*)wq, (const W*)wk, eps, whole_norm, (const int32_t*)positions, (O*)out, ldo,  \
+        (O*)k_pages, (O*)v_pages, (const int32_t*)cache_rows, n_kv, page_size)
+    if (x_dtype == BROLM_F32 && w_dtype == BROLM_F32 && out_dtype == BROLM_F32) BROLM_QN(float, float, float);
+    if (x_dtype == BROLM_F32 && w_dtype == BROLM_BF16 && out_dtype == BROLM_BF16) BROLM_QN(float, bf16, bf16);
+    if (x_dtype == BROLM_F32 && w_dtype == BROLM_F32 && out_dtype == BROLM_BF16) BROLM_QN(float, float, bf16);
+    if (x_dtype == BROLM_BF16 && w_dtype == BROLM_BF16 && out_dtype == BROLM_BF16) BROLM_QN(bf16, bf16, bf16);
+#undef BROLM_QN
+    return BROLM_ERR_BAD_DTYPE;
+}
+
+BROLM_API int brolm_gate_group_norm(const void* y, long ldy, const void* z, int z_dtype, long ldz, const void* w, int w_dtype,
+                                    float eps, int groups, int group_size, void* out, int out_dtype, long ldo, int tokens,
+                                    cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (groups <= 0 || group_size <= 0) return BROLM_ERR_BAD_SIZE;
+    if (groups > 65535) return BROLM_ERR_TOO_LARGE;
+    dim3 grid(tokens, groups);
+#define BROLM_GN(Z, W, O) return launch_pdl(gate_group_norm_kernel<Z, W, O>, grid, dim3(256), 0, stream, (const float*)y, ldy, \
+                                            (const Z*)z, ldz, (const W*)w, eps, group_size, (O*)out, ldo)
+    if (z_dtype == BROLM_F32 && w_dtype == BROLM_F32 && out_dtype == BROLM_F32) BROLM_GN(float, float, float);
+    if (z_dtype == BROLM_F32 && w_dtype == BROLM_BF16 && out_dtype == BROLM_BF16) BROLM_GN(float, bf16, bf16);
+    if (z_dtype == BROLM_F32 && w_dtype == BROLM_F32 && out_dtype == BROLM_BF16) BROLM_GN(float, float, bf16);
+    if (z_dtype == BROLM_BF16 && w_dtype == BROLM_BF16 && out_dtype == BROLM_BF16) BROLM_GN(bf16, bf16, bf16);
+#undef BROLM_GN
+    return BROLM_ERR_BAD_DTYPE;
+}
+
+BROLM_API int brolm_experts_combine(const void* y, const void* ids, const void* wts, int top, int n_real, const void* x,
+                                    int x_dtype, long ldx, const void* shared, int shared_parts, long long shared_stride,
+                                    void* out, int tokens, int hidden, cudaStream_t stream) {
+    if (tokens <= 0) return BROLM_OK;
+    if (!shared) shared_parts = 0;
+    dim3 grid(tokens, (hidden + 255) / 256);
+    if (x_dtype == BROLM_F32)
+        return launch_pdl(experts_combine_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
+                          (const float*)wts, top, n_real, (const float*)x, ldx, (const float*)shared, shared_parts,
+                          shared_stride, (float*)out, tokens, hidden);
+    if (x_dtype == BROLM_BF16)
+        return launch_pdl(experts_combine_kernel<bf16>, grid, dim3(256), 0, stream, (const float*)y, (const int32_t*)ids,
+                          (const float*)wts, top, n_real, (const bf16*)x, ldx, (const float*)shared, shared_parts,
+                          shared_stride, (float*)out, tokens, hidden);
+    return BROLM_ERR_BAD_DTYPE;
+}

@@ -277,25 +277,44 @@ def latent_rows(proj: torch.Tensor, q_cols: int, positions: torch.Tensor, cos_si
              _ptr(pages), _ptr(cache_rows) if pages is not None else None, proj.shape[0], _stream()), "latent_rows")
 
 
-def route_topk(x: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
-    """ids, weights [tokens, top]: the ``top`` experts with the largest router.x (float32 sums; ties: the lower
-    index), best first, and the logistic function of their scores."""
+ROUTE_MODES = {"logistic": 0, "softmax": 1}
+
+
+def _check_route(mode: str, correction: Optional[torch.Tensor], experts: int) -> None:
+    if mode not in ROUTE_MODES:
+        raise KernelError(f"router: unknown mode '{mode}' (known: {sorted(ROUTE_MODES)})")
+    if correction is not None:
+        assert mode == "softmax" and correction.dtype == torch.float32 and correction.is_contiguous()
+        assert correction.numel() == experts
+
+
+def route_topk(x: torch.Tensor, router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor,
+               mode: str = "logistic", correction: Optional[torch.Tensor] = None) -> None:
+    """ids, weights [tokens, top]: the ``top`` experts with the largest score, best first (ties: the lower index).
+    ``mode`` "logistic": the score is z = router.x (float32 sums) and the weight its logistic function.
+    ``mode`` "softmax": s = softmax(z) over all experts, the choice goes by s + ``correction`` (float32 [experts],
+    no part of the weights) and the weights are the chosen s over their sum (+ 1e-20)."""
     assert x.dtype == router.dtype and x.stride(1) == 1 and router.is_contiguous() and router.shape[1] == x.shape[1]
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
     assert ids.shape == (x.shape[0], top) and weights.shape == ids.shape
+    _check_route(mode, correction, router.shape[0])
     f = _fn("grouped", "brolm_route_topk", [c_int, c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                                            c_void_p, c_void_p])
+                                            c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_code(x), _ptr(x), x.stride(0), _ptr(router), x.shape[0], router.shape[0], x.shape[1], top, _ptr(ids),
-             _ptr(weights), _stream()), "route_topk")
+             _ptr(weights), ROUTE_MODES[mode], _ptr(correction), _stream()), "route_topk")
 
 
-def route_pick(z: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+def route_pick(z: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, mode: str = "logistic",
+               correction: Optional[torch.Tensor] = None) -> None:
     """The choice of ``route_topk`` from scores z [tokens, experts] float32 that a matrix product left in memory."""
     assert z.dtype == torch.float32 and z.dim() == 2 and z.stride(1) == 1 and z.shape[1] <= 1024
     assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
     assert ids.shape == (z.shape[0], top) and weights.shape == ids.shape
-    f = _fn("grouped", "brolm_route_pick", [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
-    _check(f(_ptr(z), z.stride(0), z.shape[0], z.shape[1], top, _ptr(ids), _ptr(weights), _stream()), "route_pick")
+    _check_route(mode, correction, z.shape[1])
+    f = _fn("grouped", "brolm_route_pick", [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                            c_void_p])
+    _check(f(_ptr(z), z.stride(0), z.shape[0], z.shape[1], top, _ptr(ids), _ptr(weights), ROUTE_MODES[mode],
+             _ptr(correction), _stream()), "route_pick")
 
 
 GROUP_ROWS = 64          # rows of a tile of the grouped product
@@ -359,7 +378,7 @@ def experts_linear_tc(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, 
     if down:
         assert out.dtype == torch.float32 and tuple(out.shape) == (top, tokens, N)
     else:
-        assert scale is not None and scale.dtype == torch.float32 and scale.numel() == pairs and scale.is_contiguous()
+        assert scale is None or (scale.dtype == torch.float32 and scale.numel() == pairs and scale.is_contiguous())
         assert tuple(out.shape) == (pairs, N) and out.dtype in (torch.float32, torch.bfloat16)
     if activation not in EXPERT_ACTS:
         raise KernelError(f"experts_linear_tc: unknown activation '{activation}' (known: {sorted(EXPERT_ACTS)})")
@@ -415,7 +434,7 @@ def experts_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, per
     if down:
         assert out.dtype == torch.float32 and tuple(out.shape) == (top, tokens, N) and a.shape[0] == pairs
     else:
-        assert scale is not None and scale.dtype == torch.float32 and scale.numel() == pairs and scale.is_contiguous()
+        assert scale is None or (scale.dtype == torch.float32 and scale.numel() == pairs and scale.is_contiguous())
         assert tuple(out.shape) == (pairs, N) and a.shape[0] == tokens and out.dtype in (torch.float32, a.dtype)
     if activation not in EXPERT_ACTS:
         raise KernelError(f"experts_linear: unknown activation '{activation}' (known: {sorted(EXPERT_ACTS)})")
@@ -425,6 +444,193 @@ def experts_linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, per
     _check(f(_code(a), 1 if down else 0, _ptr(a), a.stride(0), _ptr(weight), K, N * K, E, _ptr(out), N,
              1 if out.dtype == torch.float32 else 0, EXPERT_ACTS[activation], N, K, _ptr(tiles[0]), _ptr(tiles[1]),
              _ptr(offsets), _ptr(perm), _ptr(scale), top, tokens, tiles.shape[1], _stream()), "experts_linear")
+
+
+# --- row-wise steps (csrc/rowwise.cu) ---------------------------------------
+ROW_ACTS = {"none": 0, "relu2": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def cast(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x in out's element type (float32 or bfloat16)."""
+    assert x.is_contiguous() and out.is_contiguous() and x.numel() == out.numel()
+    f = _fn("rowwise", "brolm_cast", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(x), _code(x), _ptr(out), _code(out), x.numel(), _stream()), "cast")
+
+
+def bias_act(y: torch.Tensor, bias: Optional[torch.Tensor], activation: str, out: torch.Tensor) -> None:
+    """out (rows, cols) = act(y + bias); y may be [parts, rows, cols] partial sums, which are added in order first."""
+    if activation not in ROW_ACTS:
+        raise KernelError(f"bias_act: unknown activation '{activation}' (known: {sorted(ROW_ACTS)})")
+    n_parts, part_stride = (y.shape[0], y.stride(0)) if y.dim() == 3 else (1, 0)
+    rows, cols = out.shape
+    assert tuple(y.shape[-2:]) == (rows, cols) and y.stride(-1) == 1 and out.stride(1) == 1
+    if bias is not None:
+        assert bias.is_contiguous() and bias.numel() == cols
+    f = _fn("rowwise", "brolm_bias_act", [c_void_p, c_int, c_int, c_longlong, c_long, c_void_p, c_int, c_int, c_void_p, c_int,
+                                          c_long, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), _code(y), n_parts, part_stride, y.stride(-2), _ptr(bias), _code(bias) if bias is not None else F32,
+             ROW_ACTS[activation], _ptr(out), _code(out), out.stride(0), rows, cols, _stream()), "bias_act")
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b, float32; a and b may each be [parts, rows, cols] partial sums."""
+    for t in (a, b):
+        assert t.dtype == torch.float32 and t.is_contiguous() and tuple(t.shape[-2:]) == tuple(out.shape)
+    assert out.dtype == torch.float32 and out.is_contiguous()
+    ap, astr = (a.shape[0], a.stride(0)) if a.dim() == 3 else (1, 0)
+    bp, bstr = (b.shape[0], b.stride(0)) if b.dim() == 3 else (1, 0)
+    f = _fn("rowwise", "brolm_scaled_sum", [c_void_p, c_int, c_longlong, c_float, c_void_p, c_int, c_longlong, c_float,
+                                            c_void_p, c_longlong, c_void_p])
+    _check(f(_ptr(a), ap, astr, sa, _ptr(b), bp, bstr, sb, _ptr(out), out.numel(), _stream()), "scaled_sum")
+
+
+def qkv_norm_write(proj: torch.Tensor, q_cols: int, k_cols: int, v_cols: int, q_gain: Optional[torch.Tensor],
+                   k_gain: Optional[torch.Tensor], eps: float, positions: torch.Tensor, out: torch.Tensor, n_kv: int,
+                   k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                   cache_rows: Optional[torch.Tensor] = None, page_size: int = 64) -> None:
+    """proj (tokens, q_cols + k_cols + v_cols) -> out of the same layout in out's element type, the whole query
+    row and the whole key row each RMS-normed over all of their heads at once when gains are given, and keys and
+    values written into the cache pages (k rows of k_cols / n_kv, value rows of v_cols / n_kv)."""
+    assert proj.stride(1) == 1 and out.stride(1) == 1 and proj.shape == out.shape
+    assert proj.shape[1] == q_cols + k_cols + v_cols
+    assert positions.dtype == torch.int32 and positions.numel() == proj.shape[0]
+    whole = q_gain is not None
+    if whole:
+        assert k_gain is not None and q_gain.dtype == k_gain.dtype and q_gain.numel() == q_cols and k_gain.numel() == k_cols
+        assert q_gain.is_contiguous() and k_gain.is_contiguous()
+    if k_pages is not None:
+        assert v_pages is not None and cache_rows is not None and k_pages.dtype == out.dtype and v_pages.dtype == out.dtype
+        assert k_pages.is_contiguous() and v_pages.is_contiguous()
+        assert tuple(k_pages.shape[1:]) == (n_kv, page_size, k_cols // n_kv)
+        assert tuple(v_pages.shape[1:]) == (n_kv, page_size, v_cols // n_kv)
+        assert cache_rows.dtype == torch.int32 and cache_rows.numel() == proj.shape[0]
+    f = _fn("rowwise", "brolm_qkv_norm_write", [c_void_p, c_int, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+                                                c_float, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p, c_void_p,
+                                                c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), _code(proj), proj.stride(0), q_cols, k_cols, v_cols, _ptr(q_gain), _ptr(k_gain),
+             _code(q_gain) if whole else F32, eps, 1 if whole else 0, _ptr(positions), _ptr(out), _code(out), out.stride(0),
+             _ptr(k_pages), _ptr(v_pages), _ptr(cache_rows) if k_pages is not None else None, n_kv, page_size,
+             proj.shape[0], _stream()), "qkv_norm_write")
+
+
+def gate_group_norm(y: torch.Tensor, z: torch.Tensor, gain: torch.Tensor, eps: float, groups: int,
+                    out: torch.Tensor) -> None:
+    """out = rmsnorm over each of ``groups`` equal parts of (y * silu(z)), times gain.  y float32 (tokens, n);
+    z (tokens, n) may be a strided view."""
+    n = y.shape[1]
+    assert y.dtype == torch.float32 and y.stride(1) == 1 and z.stride(1) == 1 and out.stride(1) == 1
+    assert z.shape == y.shape and out.shape == y.shape and n % groups == 0 and gain.is_contiguous() and gain.numel() == n
+    f = _fn("rowwise", "brolm_gate_group_norm", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_float, c_int,
+                                                 c_int, c_void_p, c_int, c_long, c_int, c_void_p])
+    _check(f(_ptr(y), y.stride(0), _ptr(z), _code(z), z.stride(0), _ptr(gain), _code(gain), eps, groups, n // groups,
+             _ptr(out), _code(out), out.stride(0), y.shape[0], _stream()), "gate_group_norm")
+
+
+def experts_combine(y: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor, n_real: int, x: torch.Tensor,
+                    shared: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t] = sum over t's choices c of weights[t, c] * (y[c, t] if ids[t, c] < n_real else x[t]) + shared[t].
+    y float32 [top, tokens, hidden] (None when there is no real expert); shared float32 (tokens, hidden) or
+    [parts, tokens, hidden], or None."""
+    tokens, top = ids.shape
+    hidden = out.shape[1]
+    assert ids.dtype == torch.int32 and weights.dtype == torch.float32 and ids.is_contiguous() and weights.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[0] == tokens and x.stride(1) == 1
+    if y is not None:
+        assert y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (top, tokens, hidden)
+    else:
+        assert n_real == 0
+    sp, sstr = 0, 0
+    if shared is not None:
+        assert shared.dtype == torch.float32 and shared.is_contiguous() and tuple(shared.shape[-2:]) == (tokens, hidden)
+        sp, sstr = (shared.shape[0], shared.stride(0)) if shared.dim() == 3 else (1, 0)
+    f = _fn("rowwise", "brolm_experts_combine", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_long,
+                                                 c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(y), _ptr(ids), _ptr(weights), top, n_real, _ptr(x), _code(x), x.stride(0), _ptr(shared), sp, sstr,
+             _ptr(out), tokens, hidden, _stream()), "experts_combine")
+
+
+# --- mixers with a state (csrc/recurrent.cu) --------------------------------
+CONV_ACTS = {"none": 0, "silu": 1}
+
+
+def _seq(ctx_cu_q, kv_len, slots, state):
+    assert ctx_cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32 and slots.dtype == torch.int32
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    return _ptr(ctx_cu_q), _ptr(kv_len), _ptr(slots), _ptr(state), state.stride(0)
+
+
+def causal_conv(x: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor, bias: Optional[torch.Tensor],
+                activation: str, tok_seq: torch.Tensor, positions: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                slots: torch.Tensor, state: torch.Tensor, tail_off: int, out: torch.Tensor) -> None:
+    """out (tokens, C) float32 = act(causal convolution per channel of (x + in_bias) + bias).  ``taps`` float32
+    (C, K), column K - 1 weighs the token itself.  Inputs before the step come from the K - 1 rows that
+    ``state[slot, tail_off:]`` keeps as [K - 1, C] (zeros before a sequence's start); ``conv_tail`` moves them on."""
+    C, K = taps.shape
+    assert x.stride(1) == 1 and x.shape[1] == C and out.dtype == torch.float32 and out.stride(1) == 1
+    assert tuple(out.shape) == (x.shape[0], C) and taps.dtype == torch.float32 and taps.is_contiguous()
+    for v in (in_bias, bias):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == C)
+    assert tok_seq.dtype == torch.int32 and positions.dtype == torch.int32 and positions.numel() == x.shape[0]
+    assert tail_off + (K - 1) * C <= state.shape[1]
+    if activation not in CONV_ACTS:
+        raise KernelError(f"causal_conv: unknown activation '{activation}'")
+    f = _fn("recurrent", "brolm_causal_conv", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_long,
+                                               c_void_p, c_long, c_int, c_void_p])
+    _check(f(_ptr(x), _code(x), x.stride(0), _ptr(in_bias), _ptr(taps), _ptr(bias), C, K, CONV_ACTS[activation],
+             _ptr(tok_seq), _ptr(positions), *_seq(cu_q, kv_len, slots, state), tail_off, _ptr(out), out.stride(0),
+             x.shape[0], _stream()), "causal_conv")
+
+
+def conv_tail(x: torch.Tensor, in_bias: Optional[torch.Tensor], K: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
+              slots: torch.Tensor, state: torch.Tensor, tail_off: int, batch: int) -> None:
+    """Move every sequence's kept K - 1 convolution inputs on by the step's tokens (after all that read them)."""
+    C = x.shape[1]
+    assert x.stride(1) == 1 and tail_off + (K - 1) * C <= state.shape[1]
+    assert in_bias is None or (in_bias.dtype == torch.float32 and in_bias.numel() == C)
+    f = _fn("recurrent", "brolm_conv_tail", [c_void_p, c_int, c_long, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_long, c_long, c_int, c_void_p])
+    _check(f(_ptr(x), _code(x), x.stride(0), _ptr(in_bias), C, K, *_seq(cu_q, kv_len, slots, state), tail_off, batch,
+             _stream()), "conv_tail")
+
+
+def gated_scan(pre: torch.Tensor, u: torch.Tensor, y_raw: torch.Tensor, y_bias: Optional[torch.Tensor],
+               r_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor, decay_scale: float, block: int,
+               cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+               batch: int) -> None:
+    """The gated diagonal recurrence over the packed tokens: per channel c of block c // block,
+    r, i = sigmoid(pre[t, blk, 0 / 1, o] + bias), a = exp(-decay_scale * r * softplus(lam)),
+    S <- a S + sqrt(1 - a^2) i u[t, c], out[t, c] = S * gelu_tanh(y_raw[t, c] + y_bias).  S is ``state[slot, :width]``."""
+    width = u.shape[1]
+    assert pre.dtype == torch.float32 and u.dtype == torch.float32 and pre.stride(1) == 1 and u.stride(1) == 1
+    assert pre.shape[1] == 2 * width and y_raw.stride(1) == 1 and y_raw.shape[1] == width and out.stride(1) == 1
+    for v in (y_bias, r_bias, i_bias, lam):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == width)
+    f = _fn("recurrent", "brolm_gated_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_void_p])
+    _check(f(_ptr(pre), pre.stride(0), _ptr(u), u.stride(0), _ptr(y_raw), _code(y_raw), y_raw.stride(0), _ptr(y_bias),
+             _ptr(r_bias), _ptr(i_bias), _ptr(lam), decay_scale, width, block, *_seq(cu_q, kv_len, slots, state),
+             _ptr(out), _code(out), out.stride(0), batch, _stream()), "gated_scan")
+
+
+def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d: torch.Tensor,
+             heads: int, groups: int, head_size: int, n_state: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
+             slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, batch: int) -> None:
+    """The selective state space over the packed tokens.  xbc float32 (tokens, heads * P + 2 * groups * N) =
+    [x | B | C]; dt_raw (tokens, heads) may be a strided view; per head S (kept as [P][N] in ``state[slot]``):
+    dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d x."""
+    P, N = head_size, n_state
+    assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and xbc.shape[1] == heads * P + 2 * groups * N
+    assert dt_raw.stride(1) == 1 and dt_raw.shape[1] == heads and y.dtype == torch.float32 and y.stride(1) == 1
+    assert y.shape[1] == heads * P and state.shape[1] >= heads * P * N
+    for v in (dt_bias, a_log, d):
+        assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
+    f = _fn("recurrent", "brolm_ssm_scan", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_int,
+                                            c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p,
+                                            c_long, c_int, c_void_p])
+    _check(f(_ptr(xbc), xbc.stride(0), _ptr(dt_raw), _code(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(d),
+             heads, groups, P, N, *_seq(cu_q, kv_len, slots, state), _ptr(y), y.stride(0), batch, _stream()), "ssm_scan")
 
 
 def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -753,29 +959,34 @@ def attention_simt(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, kv_le
                    k: Optional[torch.Tensor] = None, v: Optional[torch.Tensor] = None,
                    k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                    page_table: Optional[torch.Tensor] = None, ring: int = 0, page_size: int = 0,
-                   sink: Optional[torch.Tensor] = None) -> None:
+                   sink: Optional[torch.Tensor] = None, v_dim: Optional[int] = None, chunk: int = 0) -> None:
     """Exact attention on CUDA cores.  Keys come from (k, v) packed like q, or from cache pages.
-    ``sink``: float32 [query heads]; exp(sink) joins every softmax's denominator (a key with no value)."""
+    ``sink``: float32 [query heads]; exp(sink) joins every softmax's denominator (a key with no value).
+    ``v_dim``: size of a value row and of an output row when it is not ``head_dim``.
+    ``chunk`` > 0: a query at position p sees no key before p - p % chunk."""
     _check_sink(sink, n_kv * group)
+    vd = v_dim or head_dim
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and q.dtype == out.dtype
     assert cu_q.dtype == torch.int32 and kv_len.dtype == torch.int32
-    kv_stride = pt_stride = 0
+    kv_stride = v_stride = pt_stride = 0
     if k_pages is not None:
         assert page_table is not None and page_table.dtype == torch.int32 and page_table.stride(1) == 1
         assert k_pages.dtype == q.dtype and v_pages.dtype == q.dtype and k_pages.is_contiguous() and v_pages.is_contiguous()
         assert tuple(k_pages.shape[1:]) == (n_kv, page_size, head_dim)
+        assert tuple(v_pages.shape[1:]) == (n_kv, page_size, vd)
         pt_stride = page_table.stride(0)
     else:
         assert k is not None and v is not None and k.dtype == q.dtype and v.dtype == q.dtype
-        assert k.stride(-1) == 1 and v.stride(-1) == 1 and k.stride(0) == v.stride(0)
-        kv_stride = k.stride(0)
+        assert k.stride(-1) == 1 and v.stride(-1) == 1
+        kv_stride, v_stride = k.stride(0), v.stride(0)
     f = _fn("attn_simt", "brolm_attn_simt", [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int, c_int,
-                                             c_void_p])
+                                             c_int, c_int, c_int, c_void_p])
     _check(f(_code(q), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k), _ptr(v),
              kv_stride, _ptr(k_pages), _ptr(v_pages), _ptr(page_table), pt_stride, ring, page_size, n_kv, group,
-             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, _stream()), "attention_simt")
+             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, vd, v_stride, int(chunk), _stream()),
+           "attention_simt")
 
 
 def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:
@@ -947,4 +1158,5 @@ __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "devi
            "experts_linear", "rmsnorm", "residual_rmsnorm",
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",
-           "decode_splits", "argmax", "sample"]
+           "decode_splits", "argmax", "sample", "cast", "bias_act", "scaled_sum", "qkv_norm_write", "gate_group_norm",
+           "experts_combine", "causal_conv", "conv_tail", "gated_scan", "ssm_scan"]

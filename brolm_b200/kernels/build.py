@@ -44,6 +44,8 @@ LIBRARIES: dict[str, list[str]] = {
     "latent": ["latent.cu"],
     "grouped": ["grouped.cu"],
     "grouped_tc": ["grouped_tc.cu"],
+    "rowwise": ["rowwise.cu"],
+    "recurrent": ["recurrent.cu"],
 }
 HEADERS = ["common.cuh", "attn_mma.cuh", "attn_decode_noalloc.h", "tcgen05.cuh"]
 

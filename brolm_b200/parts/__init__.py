@@ -1,16 +1,18 @@
 from .attention import Attention
 from .base import ParamSpec, Part, PartSpec, part_class, register_part, registered_parts
-from .block import Block, BlockSpec, ParallelBlock
+from .block import Block, BlockSpec, ParallelBlock, PostNormBlock
 from .experts import RoutedExperts
-from .feedforward import GatedFeedForward
+from .feedforward import DenseFeedForward, GatedFeedForward
 from .latent_attention import LatentAttention
 from .layout import EmbeddingSpec, HeadSpec, LayerCall, ModelLayout, PairTableSpec
 from .linear import linear
-from .norm import RMSNorm, add_then_norm
+from .norm import Cast, RMSNorm, add_then_norm
 from .position import RotaryEmbedding
+from .recurrent import GatedRecurrence, SideBySide, StateSpace
 from .stream import ConcatLinear
 
 __all__ = ["Attention", "ParamSpec", "Part", "PartSpec", "part_class", "register_part", "registered_parts", "Block",
            "BlockSpec", "GatedFeedForward", "EmbeddingSpec", "HeadSpec", "LayerCall", "ModelLayout", "linear",
            "RMSNorm", "add_then_norm", "RotaryEmbedding", "ParallelBlock", "RoutedExperts", "LatentAttention",
-           "PairTableSpec", "ConcatLinear"]
+           "PairTableSpec", "ConcatLinear", "PostNormBlock", "DenseFeedForward", "Cast", "GatedRecurrence", "SideBySide",
+           "StateSpace"]

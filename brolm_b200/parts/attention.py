@@ -7,6 +7,15 @@ projection without bias, rotation of q and k at the absolute position, k and
 v into the cache, scores = q.k * scale -> cap * tanh(./cap) -> causal/window
 mask -> softmax, then the output projection.  Key j is visible from position
 p iff 0 <= p - j < window.
+
+Options beside those: value heads of a size of their own (``v_dim``); an RMS
+norm of the whole query row and of the whole key row, one statistic over all
+heads, with a gain per element (``qk_norm="whole"``, tensors ``q_norm`` and
+``k_norm``); a chunked mask (``chunk`` = C: key j is visible from p iff j <= p
+and j >= p - p % C, chunks counted from position 0), kept in the cache as a
+ring of C places like a window.  A layer that uses one of them runs its
+projection with a float result, the row-wise kernel that norms and fills the
+cache, and the exact attention kernel.
 """
 from __future__ import annotations
 
@@ -25,22 +34,41 @@ class Attention(Part):
     graph_safe = True
 
     def __init__(self, hidden: int, n_q: int, n_kv: int, head_dim: int, scale: float, softcap: float = 0.0,
-                 window: Optional[int] = None, position: Optional[Part] = None):
+                 window: Optional[int] = None, position: Optional[Part] = None, v_dim: Optional[int] = None,
+                 qk_norm: str = "none", eps: float = 0.0, chunk: Optional[int] = None):
         if n_q % n_kv:
             raise ValueError("attention: the number of query heads must be a multiple of the kv heads")
-        if head_dim % 16:
-            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of 16; the kernels refuse it")
+        plain = not (v_dim and v_dim != head_dim) and qk_norm == "none" and not chunk
+        if head_dim % (16 if plain else 8):
+            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of {16 if plain else 8}; the kernels "
+                             f"refuse it")
         if head_dim > 512:
             raise ValueError(f"attention: head_dim {head_dim} is beyond the kernels' limit of 512")
+        if qk_norm not in ("none", "whole"):
+            raise ValueError(f"attention: unknown qk_norm '{qk_norm}' (none, whole)")
         self.hidden, self.n_q, self.n_kv, self.head_dim = hidden, n_q, n_kv, head_dim
+        self.v_dim = int(v_dim) if v_dim else head_dim
         self.scale, self.softcap = float(scale), float(softcap or 0.0)
         self.window = int(window) if window else None
+        self.chunk = int(chunk) if chunk else None
+        self.qk_norm, self.eps = qk_norm, float(eps)
         self.position = position
-        self.q_dim, self.kv_dim = n_q * head_dim, n_kv * head_dim
+        self.q_dim, self.kv_dim, self.v_cols = n_q * head_dim, n_kv * head_dim, n_kv * self.v_dim
+        # the options of the second paragraph above: their own row-wise kernel and the exact attention
+        self.rowwise = self.v_dim != head_dim or qk_norm != "none" or self.chunk is not None
+        if self.rowwise:
+            if self.v_dim % 8 or self.v_dim > 512 or head_dim % 8:
+                raise ValueError(f"attention: v_dim {self.v_dim} must be a multiple of 8 of at most 512")
+            if position is not None:
+                raise ValueError("attention: a rotation together with v_dim, qk_norm or chunk is not built")
 
     def param_specs(self):
-        return {"q": ParamSpec((self.q_dim, self.hidden)), "k": ParamSpec((self.kv_dim, self.hidden)),
-                "v": ParamSpec((self.kv_dim, self.hidden)), "o": ParamSpec((self.hidden, self.q_dim))}
+        specs = {"q": ParamSpec((self.q_dim, self.hidden)), "k": ParamSpec((self.kv_dim, self.hidden)),
+                 "v": ParamSpec((self.v_cols, self.hidden)), "o": ParamSpec((self.hidden, self.n_q * self.v_dim))}
+        if self.qk_norm == "whole":
+            specs["q_norm"] = ParamSpec((self.q_dim,), "vector")
+            specs["k_norm"] = ParamSpec((self.kv_dim,), "vector")
+        return specs
 
     def bind(self, params):
         # one projection for q, k and v: rows [Wq; Wk; Wv]
@@ -48,9 +76,16 @@ class Attention(Part):
         dt = torch.float32 if (len(kinds) > 1 or torch.float32 in kinds) else next(iter(kinds))
         self.w_qkv = torch.cat([params["q"].to(dt), params["k"].to(dt), params["v"].to(dt)], dim=0).contiguous()
         self.w_o = params["o"]
+        self.q_gain = self.k_gain = None
+        if self.qk_norm == "whole":
+            gd = torch.float32 if params["q_norm"].dtype != params["k_norm"].dtype else params["q_norm"].dtype
+            self.q_gain, self.k_gain = params["q_norm"].to(gd).contiguous(), params["k_norm"].to(gd).contiguous()
         self.params = {}
 
     def cache_spec(self):
+        if self.rowwise:
+            return KVSpec(self.n_kv, self.head_dim, self.window, v_dim=self.v_dim if self.v_dim != self.head_dim else None,
+                          chunk=self.chunk)
         return KVSpec(self.n_kv, self.head_dim, self.window)
 
     def prepare(self, max_positions, device):
@@ -61,6 +96,8 @@ class Attention(Part):
         """x (tokens, hidden) in the step's element type -> (tokens, hidden) float32, or
         [parts, tokens, hidden] partial sums that the residual kernel adds."""
         k_pages, v_pages, table, ring, page = ctx.kv(entry)
+        if self.rowwise:
+            return self._forward_rowwise(x, ctx, entry, writes_cache)
         rot = self.position.rotary_dim if self.position is not None else 0
         cos_sin = self.position.table if self.position is not None else None
         kept = (k_pages, v_pages, ctx.cache_rows[entry.group_id]) if writes_cache else (None, None, None)
@@ -96,6 +133,29 @@ class Attention(Part):
                 raise NotImplementedError("a layer that reads another layer's windowed cache cannot take a "
                                           "prompt longer than the ring in one step")
             self.attend_paged(q, out, ctx, common, k_pages, v_pages, table, ring, page)
+        return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
+
+    def _forward_rowwise(self, x, ctx, entry, writes_cache):
+        """The path of a layer with a whole-row norm, value heads of their own size or a chunked mask."""
+        k_pages, v_pages, table, ring, page = ctx.kv(entry)
+        if ctx.mode == "prefill" and not writes_cache:
+            raise NotImplementedError("a layer of this kind that reads another layer's cache cannot take a prompt")
+        proj = linear(x, self.w_qkv, out_dtype=torch.float32)
+        qkv = proj if ctx.dtype == torch.float32 else torch.empty(proj.shape, dtype=ctx.dtype, device=x.device)
+        kept = (k_pages, v_pages, ctx.cache_rows[entry.group_id]) if writes_cache else (None, None, None)
+        kernels.qkv_norm_write(proj, self.q_dim, self.kv_dim, self.v_cols, self.q_gain, self.k_gain, self.eps,
+                               ctx.positions, qkv, self.n_kv, *kept, page)
+        q = qkv[:, :self.q_dim]
+        out = torch.empty((qkv.shape[0], self.n_q * self.v_dim), dtype=ctx.dtype, device=x.device)
+        common = dict(n_kv=self.n_kv, group=self.n_q // self.n_kv, head_dim=self.head_dim, scale=self.scale,
+                      cap=self.softcap, window=self.window or 0, batch=ctx.batch, max_q_len=ctx.max_q_len,
+                      v_dim=self.v_dim, chunk=self.chunk or 0)
+        if ctx.mode == "prefill":
+            kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=qkv[:, self.q_dim:self.q_dim + self.kv_dim],
+                                   v=qkv[:, self.q_dim + self.kv_dim:], **common)
+        else:
+            kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k_pages=k_pages, v_pages=v_pages, page_table=table,
+                                   ring=ring, page_size=page, **common)
         return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
 
     # bfloat16 runs on the tensor cores when the sizes allow; everything else, and

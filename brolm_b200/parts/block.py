@@ -131,3 +131,41 @@ class ParallelBlock(Part):
 
 
 register_part("block", "parallel", ParallelBlock)
+
+
+class PostNormBlock(Part):
+    """h += post_mixer_norm(mixer(h));  h += post_ffn_norm(ffn(h)): the sublayers read the residual stream itself
+    and only their results are normed.  ``entry`` is the part that hands a sublayer its input (the stream in the
+    step's element type; the ``cast`` norm); the block before fuses it with its last sum like any entry norm."""
+
+    kind = "block"
+
+    def __init__(self, mixer: Part, post_mixer_norm: Part, entry: Part, feedforward: Optional[Part] = None,
+                 post_ffn_norm: Optional[Part] = None):
+        if (feedforward is None) != (post_ffn_norm is None):
+            raise ValueError("block: a feed-forward and the norm of its result come together")
+        self.mixer, self.feedforward, self.entry = mixer, feedforward, entry
+        self.post_mixer_norm, self.post_ffn_norm = post_mixer_norm, post_ffn_norm
+
+    def parts(self) -> dict[str, Optional[Part]]:
+        return {"mixer": self.mixer, "feedforward": self.feedforward, "entry": self.entry,
+                "post_mixer_norm": self.post_mixer_norm, "post_ffn_norm": self.post_ffn_norm}
+
+    @property
+    def entry_norm(self) -> Optional[Part]:
+        return self.entry
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, h: torch.Tensor, x: torch.Tensor, ctx, entry, writes_cache: bool,
+                next_norm: Optional[Part]) -> Optional[torch.Tensor]:
+        y = self.mixer.forward(x, ctx, entry, writes_cache)
+        if self.feedforward is None:
+            return add_then_norm(h, y, self.post_mixer_norm, next_norm, ctx.dtype)
+        x = add_then_norm(h, y, self.post_mixer_norm, self.entry, ctx.dtype)
+        y = self.feedforward.forward(x, ctx)
+        return add_then_norm(h, y, self.post_ffn_norm, next_norm, ctx.dtype)
+
+
+register_part("block", "postnorm", PostNormBlock)

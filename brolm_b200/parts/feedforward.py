@@ -51,3 +51,45 @@ class GatedFeedForward(Part):
 
 
 register_part("feedforward", "gated", GatedFeedForward)
+
+
+class DenseFeedForward(Part):
+    """down(act(up(x) + b_up)) + b_down: one hidden layer, no gate, biases optional.  ``activation``: "relu2"
+    (the square of relu), "gelu_tanh", "silu" or "none".  The products' float32 sums take bias and activation
+    in one row-wise pass."""
+
+    kind = "feedforward"
+    graph_safe = True
+
+    def __init__(self, hidden: int, inter: int, activation: str = "relu2", bias: bool = True):
+        if activation not in kernels.ROW_ACTS:
+            raise ValueError(f"feed-forward: unknown activation '{activation}'")
+        self.hidden, self.inter, self.activation, self.bias = hidden, inter, activation, bool(bias)
+
+    def param_specs(self):
+        specs = {"up": ParamSpec((self.inter, self.hidden)), "down": ParamSpec((self.hidden, self.inter))}
+        if self.bias:
+            specs["up_bias"] = ParamSpec((self.inter,), "vector")
+            specs["down_bias"] = ParamSpec((self.hidden,), "vector")
+        return specs
+
+    def bind(self, params):
+        self.w_up, self.w_down = params["up"], params["down"]
+        self.b_up = params["up_bias"].float().contiguous() if self.bias else None
+        self.b_down = params["down_bias"].float().contiguous() if self.bias else None
+        self.params = {}
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """x (tokens, hidden) -> (tokens, hidden) float32 (or partial sums when there is no bias to add)."""
+        up = linear(x, self.w_up, out_dtype=torch.float32, parts_ok=True)
+        act = torch.empty((x.shape[0], self.inter), dtype=ctx.dtype, device=x.device)
+        kernels.bias_act(up, self.b_up, self.activation, act)
+        y = linear(act, self.w_down, out_dtype=torch.float32, parts_ok=True)
+        if self.b_down is None:
+            return y
+        out = torch.empty((x.shape[0], self.hidden), dtype=torch.float32, device=x.device)
+        kernels.bias_act(y, self.b_down, "none", out)
+        return out
+
+
+register_part("feedforward", "dense", DenseFeedForward)

@@ -40,6 +40,30 @@ class RMSNorm(Part):
 register_part("norm", "rmsnorm", RMSNorm)
 
 
+class Cast(Part):
+    """No norm at all: the rows as they are, in the element type asked for.  It stands where an arrangement
+    whose sublayers read the residual stream itself needs an entry "norm"; in float32 the stream is handed
+    on as it is, without a copy (every sublayer has read its input before the stream takes its result)."""
+
+    kind = "norm"
+    graph_safe = True
+
+    def __init__(self, size: int):
+        self.size = size
+
+    def apply(self, x: torch.Tensor, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is not None:
+            x = x.index_select(0, rows.long())
+        if x.dtype == out_dtype:
+            return x
+        out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        kernels.cast(x, out)
+        return out
+
+
+register_part("norm", "cast", Cast)
+
+
 def add_then_norm(h: torch.Tensor, y: torch.Tensor, post: Optional[Part], nxt: Optional[Part],
                   out_dtype: torch.dtype) -> Optional[torch.Tensor]:
     """h += post(y) (or y);  return nxt(h) when ``nxt`` is given.
