@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(256) conv_tail_kernel(const X* __restrict__ x,
 //   r = sigmoid(pre[t][blk][0][o] + rb[c]),  i = sigmoid(pre[t][blk][1][o] + ib[c])       (pre: the block-diagonal
 //   log a = -decay_scale * r * softplus(lam[c]),  a = exp(log a)                            products of u, made before)
 //   S <- a S + sqrt(1 - a^2) * i * u[t][c];   out[t][c] = S * gelu_tanh(y_raw[t][c] + yb[c])
-// 1 - a^2 is taken as -expm1(2 log a), which keeps its digits when a is close to one.
+// 1 - a^2 is taken as -expm1(2 log a) and a S as S + expm1(log a) S, which keep their digits when a is close to
+// one (a state that remembers for thousands of tokens): a itself, rounded to float, would not.
 // ---------------------------------------------------------------------------
 template <typename Y, typename O>
 __global__ void __launch_bounds__(128) gated_scan_kernel(const float* __restrict__ pre, long ldpre, const float* __restrict__ u,
@@ -140,9 +141,8 @@ __global__ void __launch_bounds__(128) gated_scan_kernel(const float* __restrict
             if (t0 + k < q_len) {
                 const float r = sigmoid_f(vr[k] + bias_r), g = sigmoid_f(vi[k] + bias_i);
                 const float log_a = sp * r;
-                const float a = expf(log_a);
                 const float drive = sqrtf(-expm1f(2.0f * log_a)) * g * vu[k];
-                S = fmaf(a, S, drive);
+                S = fmaf(expm1f(log_a), S, S) + drive;          // a S as S + (a - 1) S
                 out[(size_t)(q0 + t0 + k) * ldo + c] = from_float<O>(S * gelu_tanh_f(vy[k] + bias_y));
             }
         }
@@ -207,7 +207,7 @@ __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__
         if (threadIdx.x < n_tok) {
             const float dt = softplus_f(to_float(dt_raw[(size_t)(q0 + t0 + threadIdx.x) * lddt + h]) + dtb);
             sdt[threadIdx.x] = dt;
-            sdec[threadIdx.x] = expf(A * dt);
+            sdec[threadIdx.x] = expm1f(A * dt);            // decay - 1: the decay is applied as S + (decay - 1) S
         }
         __syncthreads();
         for (int tt = 0; tt < n_tok; ++tt) {
@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__
             for (int j = 0; j < NPT; ++j) {
                 const int n = sl + nsplit * j;
                 if (n < N) {
-                    S[j] = fmaf(dec, S[j], dx * rb[n]);
+                    S[j] = fmaf(dec, S[j], S[j]) + dx * rb[n];
                     acc = fmaf(S[j], rc[n], acc);
                 }
             }
