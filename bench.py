@@ -22,6 +22,9 @@ width, heads, window, layer runs and active feed-forward size: one prompt of 2,0
 batch 8, both through the engine, and a table of the device time of each kernel of both models with the
 main kernels' fractions of their rooflines.  One JSON line of its own shape; the default run is untouched.
 
+``--arch neburax [--size s|m]``: the same for the Neburax design (state-space layers, chunked attention beside a
+gated recurrence, routed experts with a shared expert), beside Gemma 2 at equal sizes.
+
 More than one GPU is not what this library does: ``--gpus N`` with N > 1 says
 so and exits with 2.
 """
@@ -162,6 +165,72 @@ BANEVIK_SIZES = {
 }
 
 
+def measure_design(cfg, vocab, dev, flush, steps, warmup, batch, context, prompt_len):
+    """One prompt timed alone after an L2 flush, then decode steps through the generation loop's captured step,
+    both with the device's own record of every kernel."""
+    import torch
+
+    import brolm_b200 as bb
+    from brolm_b200 import kernels
+    from brolm_b200.kernels.microbench import _cuda_events
+
+    model = bb.Model(cfg, dtype="bfloat16", device=dev).init_random(seed=0, on_device=True)
+    g = torch.Generator().manual_seed(1)
+    out = {}
+    # one prompt, timed alone after an L2 flush: the median of three after three untimed ones
+    eng = bb.Engine(model, max_tokens=prompt_len + 64, max_slots=1, max_seq_len=prompt_len + 1)
+    prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
+    times = []
+    for it in range(6):
+        (s,) = eng.open(1)
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([s], [prompt])
+        e1.record()
+        torch.cuda.synchronize()
+        eng.close([s])
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+
+    def one_prompt():
+        (s,) = eng.open(1)
+        eng.step([s], [prompt])
+        eng.close([s])
+    out["prefill_ms"] = statistics.median(times)
+    out["prefill_kernels"] = _by_kernel(_cuda_events(one_prompt))
+    del eng
+    # decoding: the generation loop's own steps, ids fed on the device
+    total = SETTLE + warmup + steps
+    eng = bb.Engine(model, max_tokens=batch * ((context + 63) // 64 * 64), max_slots=batch, max_seq_len=context + 1)
+    prompts = [torch.randint(0, vocab, (context - total - 1,), generator=g).tolist() for _ in range(batch)]
+    sampler = bb.Sampler(bb.SamplingParams(temperature=0.0))
+    streams = torch.arange(batch, dtype=torch.int32, device=dev)
+    pick = list(range(batch))
+    slots = eng.open(batch)
+    state = {"ids": sampler(eng.step(slots, prompts), streams, 0), "n": 1}
+
+    def go(n):
+        for _ in range(n):
+            state["ids"] = sampler(eng.step_from(slots, state["ids"], pick), streams, state["n"])
+            state["n"] += 1
+    go(SETTLE + warmup)
+    with ClockSampler() as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = kernels.launch_count()
+        e0.record()
+        go(steps)
+        e1.record()
+        torch.cuda.synchronize()
+    out["decode_ms"] = e0.elapsed_time(e1) / steps
+    out["launches"] = kernels.launch_count() - before
+    out["clocks"] = clocks.summary()
+    out["decode_kernels"] = _by_kernel(_cuda_events(lambda: go(1)))
+    eng.close(slots)
+    return out
+
+
+
 def banevik_main(args, pk) -> int:
     import torch
 
@@ -191,63 +260,8 @@ def banevik_main(args, pk) -> int:
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     steps, warmup, batch, context, prompt_len = args.steps or 64, max(args.warmup, 3), args.batch or 8, 1280, 2048
 
-    def measure(cfg, vocab):
-        model = bb.Model(cfg, dtype="bfloat16", device=dev).init_random(seed=0, on_device=True)
-        g = torch.Generator().manual_seed(1)
-        out = {}
-        # one prompt, timed alone after an L2 flush: the median of three after three untimed ones
-        eng = bb.Engine(model, max_tokens=prompt_len + 64, max_slots=1, max_seq_len=prompt_len + 1)
-        prompt = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
-        times = []
-        for it in range(6):
-            (s,) = eng.open(1)
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            eng.step([s], [prompt])
-            e1.record()
-            torch.cuda.synchronize()
-            eng.close([s])
-            if it >= 3:
-                times.append(e0.elapsed_time(e1))
-
-        def one_prompt():
-            (s,) = eng.open(1)
-            eng.step([s], [prompt])
-            eng.close([s])
-        out["prefill_ms"] = statistics.median(times)
-        out["prefill_kernels"] = _by_kernel(_cuda_events(one_prompt))
-        del eng
-        # decoding: the generation loop's own steps, ids fed on the device
-        total = SETTLE + warmup + steps
-        eng = bb.Engine(model, max_tokens=batch * ((context + 63) // 64 * 64), max_slots=batch, max_seq_len=context + 1)
-        prompts = [torch.randint(0, vocab, (context - total - 1,), generator=g).tolist() for _ in range(batch)]
-        sampler = bb.Sampler(bb.SamplingParams(temperature=0.0))
-        streams = torch.arange(batch, dtype=torch.int32, device=dev)
-        pick = list(range(batch))
-        slots = eng.open(batch)
-        state = {"ids": sampler(eng.step(slots, prompts), streams, 0), "n": 1}
-
-        def go(n):
-            for _ in range(n):
-                state["ids"] = sampler(eng.step_from(slots, state["ids"], pick), streams, state["n"])
-                state["n"] += 1
-        go(SETTLE + warmup)
-        with ClockSampler() as clocks:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            before = kernels.launch_count()
-            e0.record()
-            go(steps)
-            e1.record()
-            torch.cuda.synchronize()
-        out["decode_ms"] = e0.elapsed_time(e1) / steps
-        out["launches"] = kernels.launch_count() - before
-        out["clocks"] = clocks.summary()
-        out["decode_kernels"] = _by_kernel(_cuda_events(lambda: go(1)))
-        eng.close(slots)
-        return out
-
-    b, gm = measure(bcfg, z["vocab"]), measure(gcfg, z["vocab"])
+    common = (dev, flush, steps, warmup, batch, context, prompt_len)
+    b, gm = measure_design(bcfg, z["vocab"], *common), measure_design(gcfg, z["vocab"], *common)
     W, H, D, R = z["width"], z["heads"], z["kv_rank"] + z["rot_dim"], z["kv_rank"]
     T, top, ff, win = prompt_len, z["top"], z["ff"], z["window"]
     keys = win * (win + 1) // 2 + (T - win) * win if T > win else T * (T + 1) // 2
@@ -311,6 +325,116 @@ def banevik_main(args, pk) -> int:
     return 0
 
 
+# --arch neburax: a state-space layer with a dense feed-forward, a layer of chunked attention beside a gated
+# recurrence with routed experts, a state-space layer with routed experts, and the second layer's tensors once more
+NEBURAX_SIZES = {
+    "s": dict(width=2048, ssm_heads=32, ssm_vdim=128, state=128, groups=8, heads=16, kv_heads=4, dim=128, vdim=128,
+              chunk=1024, rec_width=2048, rec_blocks=8, experts=32, identity=2, top=4, ff=1024, shared=1024,
+              dense_ff=4096, vocab=32768),
+    "m": dict(width=3072, ssm_heads=48, ssm_vdim=128, state=128, groups=8, heads=24, kv_heads=4, dim=128, vdim=128,
+              chunk=2048, rec_width=3072, rec_blocks=12, experts=64, identity=2, top=6, ff=1024, shared=2048,
+              dense_ff=6144, vocab=65536),
+}
+
+
+def neburax_main(args, pk) -> int:
+    import torch
+
+    import brolm_b200 as bb
+
+    name = args.size if args.size in NEBURAX_SIZES else "s"
+    z = NEBURAX_SIZES[name]
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    W = z["width"]
+    moe = dict(kind="moe", expert=dict(ff=z["ff"]), router=dict(experts=z["experts"], top=z["top"], identity=z["identity"]),
+               shared=dict(ff=z["shared"]))
+    ssm = dict(heads=z["ssm_heads"], vdim=z["ssm_vdim"], state=z["state"], groups=z["groups"], norm_groups=z["groups"], conv=4)
+    pair = dict(left=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["dim"], vdim=z["vdim"], scale=z["dim"] ** -0.5,
+                          mask=dict(size=z["chunk"])),
+                right=dict(width=z["rec_width"], blocks=z["rec_blocks"], conv=4), left_scale=1.0, right_scale=1.0)
+    layers = [dict(type="mamba2", mixer=ssm, mlp=dict(kind="dense", ff=z["dense_ff"])),
+              dict(type="parallel", mixer=pair, mlp=moe), dict(type="mamba2", mixer=ssm, mlp=moe),
+              dict(type="parallel", mixer=pair, mlp=moe, weights_of=1)]
+    ncfg = bb.NeburaxConfig.from_dict(dict(architecture="Neburax", vocab=z["vocab"], width=W, layers=layers,
+                                           norm=dict(eps=1e-5)))
+    runs = len(layers)
+    inter = ((z["top"] * z["ff"] + z["shared"]) + 255) // 256 * 256         # a token's active feed-forward width
+    gcfg = bb.Gemma2Config(vocab_size=z["vocab"], hidden_size=W, intermediate_size=inter, num_hidden_layers=runs,
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                           query_pre_attn_scalar=float(z["dim"]), sliding_window=z["chunk"],
+                           layer_types=("sliding_attention",) * runs, max_position_embeddings=8192)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    steps, warmup, batch, context, prompt_len = args.steps or 64, max(args.warmup, 3), args.batch or 8, 1280, 2048
+    common = (dev, flush, steps, warmup, batch, context, prompt_len)
+    b, gm = measure_design(ncfg, z["vocab"], *common), measure_design(gcfg, z["vocab"], *common)
+    T, top, ff, H, G, d, dv, C = prompt_len, z["top"], z["ff"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["chunk"]
+    full, part = divmod(T, C)
+    keys = full * (C * (C + 1) // 2) + part * (part + 1) // 2                  # visible (query, key) pairs of a prompt
+    gkeys = C * (C + 1) // 2 + (T - C) * C if T > C else T * (T + 1) // 2      # ... under a window of the same size
+    nh, P, N, grp = z["ssm_heads"], z["ssm_vdim"], z["state"], z["groups"]
+    inner, cols = nh * P, nh * P + 2 * grp * N
+    tf, gb = pk["bf16_burst"] * 1e12, pk["hbm_gbs"] * 1e9
+    active = min(z["experts"], batch * top)
+    n_pair, n_ssm, n_moe = 2, 2, 3
+    # (kernel-name fragment, work of all its launches in one pass over the layers, bound)
+    rows = [
+        ("neburax prefill", b["prefill_kernels"], [
+            ("grouped_tc_kernel", n_moe * 2.0 * T * top * ff * W * 3, "flops"),
+            ("attn_prefill", n_pair * 2.0 * H * (d + dv) * keys, "flops"),
+            ("attn_simt", n_pair * 2.0 * H * (d + dv) * keys, "flops"),
+            ("ssm_", n_ssm * T * (cols + inner + nh) * 4.0, "bytes"),
+            ("gated_scan", n_pair * T * z["rec_width"] * (4 * 4.0 + 2), "bytes"),
+        ]),
+        ("closest prefill", gm["prefill_kernels"], [
+            ("gemm_tc2_kernel<1>", runs * 2.0 * T * W * 2 * inter, "flops"),
+            ("attn_prefill_tc", runs * 4.0 * H * d * gkeys, "flops"),
+        ]),
+        ("neburax decode", b["decode_kernels"], [
+            ("fast_kernel<64, 64, 4, false>", n_moe * active * ff * W * 2.0 * 3, "bytes"),
+            ("attn_decode", n_pair * batch * min(context, C) * G * (d + dv) * 2.0, "bytes"),
+            ("attn_simt", n_pair * batch * min(context, C) * G * (d + dv) * 2.0, "bytes"),
+            ("ssm_", n_ssm * batch * nh * P * N * 4.0 * 2, "bytes"),
+        ]),
+        ("closest decode", gm["decode_kernels"], [
+            ("skinny_kernel<2, 1, 1>", runs * 2 * inter * W * 2.0, "bytes"),
+            ("attn_decode_mma", runs * batch * min(context, C) * 2 * G * d * 2.0, "bytes"),
+        ]),
+    ]
+    table = []
+    for title, kern, wanted in rows:
+        for frag, work, bound in wanted:
+            us = sum(v["us"] for k, v in kern.items() if frag in k)
+            n = sum(v["n"] for k, v in kern.items() if frag in k)
+            if not n:
+                continue
+            frac = work / (us * 1e-6) / (tf if bound == "flops" else gb)
+            table.append({"step": title, "kernel": frag, "launches": n, "us": round(us, 2),
+                          "bound": "tensor" if bound == "flops" else "hbm", "frac_of_measured_peak": round(frac, 4)})
+    result = {
+        "metric": f"Neburax decode tokens/s (size {name}, batch {batch}, context {context}) beside Gemma 2 at equal sizes",
+        "value": round(batch * 1000.0 / b["decode_ms"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(b["decode_ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "impl": "brolm_b200", "clocks": b["clocks"], "gpu_launches": b["launches"],
+        "config": {"model": "Neburax", **{k: v for k, v in z.items()}, "layer_runs": runs, "global_batch": batch,
+                   "seq_len": context, "closest": {"model": "Gemma 2", "hidden": W, "heads": H, "kv_heads": G,
+                                                   "head_dim": d, "intermediate": inter, "layers": runs,
+                                                   "sliding_window": C},
+                   "l2": "the prompt is timed after an L2 flush; a decode step reads more than the L2 holds",
+                   "peaks": pk["source"]},
+        "neburax": {"prefill_tok_s": round(T * 1000.0 / b["prefill_ms"], 1), "prefill_ms": round(b["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / b["decode_ms"], 1), "decode_ms": round(b["decode_ms"], 4)},
+        "closest": {"prefill_tok_s": round(T * 1000.0 / gm["prefill_ms"], 1), "prefill_ms": round(gm["prefill_ms"], 3),
+                    "decode_tok_s": round(batch * 1000.0 / gm["decode_ms"], 1), "decode_ms": round(gm["decode_ms"], 4)},
+        "kernels": table,
+        "by_kernel_us": {"neburax_prefill": _top(b["prefill_kernels"], 24), "closest_prefill": _top(gm["prefill_kernels"]),
+                         "neburax_decode": _top(b["decode_kernels"], 24), "closest_decode": _top(gm["decode_kernels"])},
+    }
+    print(json.dumps(result))
+    return 0
+
+
 def _by_kernel(events) -> dict:
     """Device records -> {kernel name: {"us": total time, "n": launches}}."""
     out: dict = {}
@@ -329,8 +453,8 @@ def _top(kern: dict, n: int = 14) -> dict:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik"],
-                    help="banevik: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m)")
+    ap.add_argument("--arch", default="gemma2", choices=["gemma2", "banevik", "neburax"],
+                    help="banevik, neburax: that design at real layer sizes beside Gemma 2 at equal sizes (--size s|m)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=0, help="decode steps in a timed region (default 64; 128 for 9b)")
     ap.add_argument("--warmup", type=int, default=8)
@@ -354,8 +478,10 @@ def main() -> int:
         return 2
     if args.arch == "banevik":
         return banevik_main(args, peaks())
+    if args.arch == "neburax":
+        return neburax_main(args, peaks())
     if args.size not in SIZES:
-        print(f"bench.py: --size {args.size} goes with --arch banevik")
+        print(f"bench.py: --size {args.size} goes with --arch banevik or neburax")
         return 2
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)

@@ -37,7 +37,7 @@
 // * The function calls no cudaMalloc, cudaFree or any allocating routine.
 //
 // Arguments and result are those of brolm_attn_decode_mma (attn_mma.cu)
-// without the two scratch pointers.
+// without the two scratch pointers and without the chunk size (no chunked mask here).
 #pragma once
 
 #include <cuda_runtime.h>

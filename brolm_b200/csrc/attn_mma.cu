@@ -6,7 +6,7 @@
 BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int out_stride, const void* cu_q,
                                      const void* k, const void* v, int kv_stride, int n_kv, int group, int hd,
                                      float scale, float cap, int window, const void* sink, int batch,
-                                     int max_q_len, cudaStream_t stream) {
+                                     int max_q_len, int chunk, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
     int st = check_common(hd, group, n_kv, q_stride, out_stride, batch);
     if (st) return st;
@@ -14,7 +14,7 @@ BROLM_API int brolm_attn_prefill_mma(const void* q, int q_stride, void* out, int
     MmaArgs a = {};
     a.q = (const bf16*)q; a.out = (bf16*)out; a.q_stride = q_stride; a.out_stride = out_stride;
     a.cu_q = (const int32_t*)cu_q; a.k = (const bf16*)k; a.v = (const bf16*)v; a.kv_stride = kv_stride;
-    a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.n_splits = 1;
+    a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.n_splits = 1; a.chunk = chunk;
     a.sink = (const float*)sink;
     a.sms = device_sm_count();
     if (hd == 64) return launch_prefill<64, true>(a, batch, max_q_len, stream);
@@ -32,7 +32,8 @@ BROLM_API int brolm_attn_decode_mma(const void* q, int q_stride, void* out, int 
                                     const void* kv_len, const void* k_pages, const void* v_pages,
                                     const void* page_table, int pt_stride, int ring, int page_size, int n_kv,
                                     int group, int hd, float scale, float cap, int window, const void* sink,
-                                    int batch, int n_splits, void* part_o, void* part_ml, cudaStream_t stream) {
+                                    int batch, int n_splits, void* part_o, void* part_ml, int chunk,
+                                    cudaStream_t stream) {
     if (batch <= 0) return BROLM_OK;
     int st = check_common(hd, group, n_kv, q_stride, out_stride, batch);
     if (st) return st;
@@ -45,7 +46,7 @@ BROLM_API int brolm_attn_decode_mma(const void* q, int q_stride, void* out, int 
     a.cu_q = (const int32_t*)cu_q; a.kv_len = (const int32_t*)kv_len;
     a.k_pages = (const bf16*)k_pages; a.v_pages = (const bf16*)v_pages; a.page_table = (const int32_t*)page_table;
     a.pt_stride = pt_stride; a.ring = ring;
-    a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window;
+    a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.chunk = chunk;
     a.n_splits = n_splits; a.part_o = (float*)part_o; a.part_ml = (float*)part_ml;
     a.sink = (const float*)sink; a.shared_kv = k_pages == v_pages;
     if (hd == 64) return launch_decode<64, true>(a, batch, stream);

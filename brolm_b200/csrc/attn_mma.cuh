@@ -101,6 +101,7 @@ struct MmaArgs {
     int n_kv, group, hd;
     float scale, cap;
     int window;
+    int chunk;              // > 0: position p sees no key before p - p % chunk (chunks counted from position 0)
     int sms;                // SMs of the device (prompt kernel: pairing of heavy and light tiles)
     // split-KV scratch
     int n_splits;
@@ -157,7 +158,10 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int window = a.window > 0 ? a.window : 0x3fffffff;
     const int tok_lo = row0 / a.group, tok_hi = (row0 + rows_here - 1) / a.group;
-    const int key_lo = max(0, tok_lo - window + 1), key_hi = tok_hi;
+    const int chunk = a.chunk > 0 ? a.chunk : 0x3fffffff;
+    // the lowest row's chunk begins first; the highest row's begins last, and tiles below that need the mask
+    const int key_lo = max(max(0, tok_lo - window + 1), tok_lo - tok_lo % chunk), key_hi = tok_hi;
+    const int chunk_hi = tok_hi - tok_hi % chunk;
     const int t_first = key_lo / KT, t_last = key_hi / KT;
 
     // queries of this block; rows past the end read as zero
@@ -233,7 +237,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
         }
         // scale, soft-cap, mask
         const int tile_lo = t * KT, tile_hi = tile_lo + KT - 1;
-        const bool edge = tile_hi > tok_lo || tile_lo < tok_hi - window + 1;
+        const bool edge = tile_hi > tok_lo || tile_lo < tok_hi - window + 1 || tile_lo < chunk_hi;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
@@ -242,7 +246,7 @@ __global__ void __launch_bounds__(NTHREADS) attn_prefill_mma_kernel(MmaArgs a) {
                 if (edge) {
                     const int kp = tile_lo + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int p = rpos[e >> 1];
-                    if (!(p >= 0 && kp <= p && p - kp < window)) v = -INFINITY;
+                    if (!(p >= 0 && kp <= p && p - kp < window && kp >= p - p % chunk)) v = -INFINITY;
                 }
                 s[nt][e] = v;
             }
@@ -350,8 +354,9 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_mma_kernel(MmaArgs a) {
     __syncthreads();
     pdl_wait();               // q and the newest key and value come from the kernels before this one
     const int n_q = a.n_kv * a.group;
-    const int window = a.window > 0 ? a.window : 0x3fffffff;
     const int pos = kv_len - 1;
+    int window = a.window > 0 ? a.window : 0x3fffffff;
+    if (a.chunk > 0 && pos >= 0) window = min(window, pos % a.chunk + 1);     // a chunk is a window that begins anew
     const int key_lo = max(0, pos - window + 1);
     int t_begin = 0, t_end = 0;                               // tiles [t_begin, t_end) of this split
     if (kv_len > 0) {

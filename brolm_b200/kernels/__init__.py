@@ -596,22 +596,46 @@ def conv_tail(x: torch.Tensor, in_bias: Optional[torch.Tensor], K: int, cu_q: to
 
 def gated_scan(pre: torch.Tensor, u: torch.Tensor, y_raw: torch.Tensor, y_bias: Optional[torch.Tensor],
                r_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor, decay_scale: float, block: int,
-               cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
-               batch: int) -> None:
+               positions: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
+               out: torch.Tensor, batch: int, max_q_len: int) -> None:
     """The gated diagonal recurrence over the packed tokens: per channel c of block c // block,
     r, i = sigmoid(pre[t, blk, 0 / 1, o] + bias), a = exp(-decay_scale * r * softplus(lam)),
-    S <- a S + sqrt(1 - a^2) i u[t, c], out[t, c] = S * gelu_tanh(y_raw[t, c] + y_bias).  S is ``state[slot, :width]``."""
+    S <- a S + sqrt(1 - a^2) i u[t, c], out[t, c] = S * gelu_tanh(y_raw[t, c] + y_bias).  S is ``state[slot, :width]``.
+    ``pre`` is overwritten.  A sequence of more than 32 tokens is scanned as 32 runs side by side that are then joined."""
     width = u.shape[1]
     assert pre.dtype == torch.float32 and u.dtype == torch.float32 and pre.stride(1) == 1 and u.stride(1) == 1
     assert pre.shape[1] == 2 * width and y_raw.stride(1) == 1 and y_raw.shape[1] == width and out.stride(1) == 1
+    assert positions.dtype == torch.int32 and positions.numel() == u.shape[0]
     for v in (y_bias, r_bias, i_bias, lam):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == width)
     f = _fn("recurrent", "brolm_gated_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                              c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_void_p])
+                                              c_void_p, c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_int, c_int,
+                                              c_void_p])
     _check(f(_ptr(pre), pre.stride(0), _ptr(u), u.stride(0), _ptr(y_raw), _code(y_raw), y_raw.stride(0), _ptr(y_bias),
-             _ptr(r_bias), _ptr(i_bias), _ptr(lam), decay_scale, width, block, *_seq(cu_q, kv_len, slots, state),
-             _ptr(out), _code(out), out.stride(0), batch, _stream()), "gated_scan")
+             _ptr(r_bias), _ptr(i_bias), _ptr(lam), decay_scale, width, block, _ptr(positions),
+             *_seq(cu_q, kv_len, slots, state), _ptr(out), _code(out), out.stride(0), batch, u.shape[0], max_q_len,
+             _stream()), "gated_scan")
+    global _launches
+    _launches += 1                      # two kernels
+
+
+def block_matvec_ok(rows: int, k: int) -> bool:
+    """Whether ``block_matvec_f32`` takes this many rows of this length."""
+    return 0 < rows <= 16 and rows * k <= 12288
+
+
+def block_matvec_f32(a: torch.Tensor, a_head: int, weight: torch.Tensor, out: torch.Tensor, o_head: int) -> None:
+    """``heads_linear`` for a handful of float32 rows: out[t, h * o_head + n] = sum_k weight[h, n, k] * a[t, h * a_head + k],
+    one coalesced pass over every matrix row, used for all tokens."""
+    H, N, K = weight.shape
+    assert a.dtype == torch.float32 and weight.dtype == torch.float32 and out.dtype == torch.float32
+    assert weight.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and a.shape[0] == out.shape[0]
+    assert (H - 1) * a_head + K <= a.shape[1] and (H - 1) * o_head + N <= out.shape[1] and block_matvec_ok(a.shape[0], K)
+    f = _fn("recurrent", "brolm_block_matvec_f32", [c_void_p, c_long, c_long, c_void_p, c_void_p, c_long, c_long, c_int, c_int,
+                                                    c_int, c_int, c_void_p])
+    _check(f(_ptr(a), a.stride(0), a_head, _ptr(weight), _ptr(out), out.stride(0), o_head, a.shape[0], H, N, K, _stream()),
+           "block_matvec_f32")
 
 
 def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d: torch.Tensor,
@@ -622,7 +646,8 @@ def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
     dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d x."""
     P, N = head_size, n_state
     assert xbc.dtype == torch.float32 and xbc.stride(1) == 1 and xbc.shape[1] == heads * P + 2 * groups * N
-    assert dt_raw.stride(1) == 1 and dt_raw.shape[1] == heads and y.dtype == torch.float32 and y.stride(1) == 1
+    assert dt_raw.dtype == torch.float32 and dt_raw.stride(1) == 1 and dt_raw.shape[1] == heads
+    assert y.dtype == torch.float32 and y.stride(1) == 1
     assert y.shape[1] == heads * P and state.shape[1] >= heads * P * N
     for v in (dt_bias, a_log, d):
         assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
@@ -996,17 +1021,18 @@ def _check_sink(sink: Optional[torch.Tensor], n_q: int) -> None:
 
 def attention_prefill_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
                           n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int, batch: int,
-                          max_q_len: int, sink: Optional[torch.Tensor] = None) -> None:
-    """Tensor-core attention of whole prompts that start at position 0 (bfloat16, head_dim <= 256)."""
+                          max_q_len: int, sink: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
+    """Tensor-core attention of whole prompts that start at position 0 (bfloat16, head_dim <= 256).
+    ``chunk`` > 0: a query at position p sees no key before p - p % chunk."""
     _check_sink(sink, n_kv * group)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
     assert q.stride(-1) == 1 and out.stride(-1) == 1 and k.stride(-1) == 1 and v.stride(-1) == 1
     assert k.stride(0) == v.stride(0) and cu_q.dtype == torch.int32
     f = _fn("attn_mma", "brolm_attn_prefill_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                    c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_int,
-                                                   c_int, c_void_p])
+                                                   c_int, c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(k), _ptr(v), k.stride(0), n_kv, group,
-             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, _stream()), "attention_prefill_mma")
+             head_dim, scale, cap, window, _ptr(sink), batch, max_q_len, int(chunk), _stream()), "attention_prefill_mma")
 
 
 def attention_prefill_tc_ok(head_dim: int, group: int) -> bool:
@@ -1102,7 +1128,7 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
                          k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor, *, ring: int,
                          page_size: int, n_kv: int, group: int, head_dim: int, scale: float, cap: float, window: int,
                          batch: int, n_splits: int, scratch: Optional[tuple] = None,
-                         sink: Optional[torch.Tensor] = None) -> None:
+                         sink: Optional[torch.Tensor] = None, chunk: int = 0) -> None:
     """Tensor-core attention of one new token per sequence over the paged cache
     (bfloat16, head_dim <= 256, group <= 16, pages of 64 keys).  With more than
     one split the partial results go through float32 scratch: ``scratch`` =
@@ -1129,10 +1155,10 @@ def attention_decode_mma(q: torch.Tensor, out: torch.Tensor, cu_q: torch.Tensor,
     f = _fn("attn_mma", "brolm_attn_decode_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                                   c_float, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                                  c_void_p])
+                                                  c_int, c_void_p])
     _check(f(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(cu_q), _ptr(kv_len), _ptr(k_pages), _ptr(v_pages),
              _ptr(page_table), page_table.stride(0), ring, page_size, n_kv, group, head_dim, scale, cap, window,
-             _ptr(sink), batch, n_splits, _ptr(part_o), _ptr(part_ml), _stream()), "attention_decode_mma")
+             _ptr(sink), batch, n_splits, _ptr(part_o), _ptr(part_ml), int(chunk), _stream()), "attention_decode_mma")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -1159,4 +1185,4 @@ __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "devi
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample", "cast", "bias_act", "scaled_sum", "qkv_norm_write", "gate_group_norm",
-           "experts_combine", "causal_conv", "conv_tail", "gated_scan", "ssm_scan"]
+           "experts_combine", "causal_conv", "conv_tail", "gated_scan", "ssm_scan", "block_matvec_f32", "block_matvec_ok"]

@@ -150,9 +150,19 @@ class Attention(Part):
         common = dict(n_kv=self.n_kv, group=self.n_q // self.n_kv, head_dim=self.head_dim, scale=self.scale,
                       cap=self.softcap, window=self.window or 0, batch=ctx.batch, max_q_len=ctx.max_q_len,
                       v_dim=self.v_dim, chunk=self.chunk or 0)
-        if ctx.mode == "prefill":
-            kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=qkv[:, self.q_dim:self.q_dim + self.kv_dim],
-                                   v=qkv[:, self.q_dim + self.kv_dim:], **common)
+        # bfloat16 with key and value rows of one size runs on the tensor cores; all else on the exact kernel
+        tensor = self._tensor_cores(ctx) and self.v_dim == self.head_dim and self.head_dim % 16 == 0
+        k, v = qkv[:, self.q_dim:self.q_dim + self.kv_dim], qkv[:, self.q_dim + self.kv_dim:]
+        if ctx.mode == "prefill" and tensor:
+            kernels.attention_prefill_mma(q, out, ctx.cu_q, k, v, **{n: a for n, a in common.items() if n != "v_dim"})
+        elif ctx.mode == "prefill":
+            kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k=k, v=v, **common)
+        elif tensor and page == 64:
+            span = min(self.window or (1 << 30), self.chunk or (1 << 30))
+            splits = kernels.decode_splits(ctx.batch, self.n_kv, ctx.max_kv_len, span if span < (1 << 30) else 0,
+                                           ragged=getattr(ctx, "ragged", False))
+            kernels.attention_decode_mma(q, out, ctx.cu_q, ctx.kv_len, k_pages, v_pages, table, ring=ring, page_size=page,
+                                         n_splits=splits, **{n: a for n, a in common.items() if n not in ("v_dim", "max_q_len")})
         else:
             kernels.attention_simt(q, out, ctx.cu_q, ctx.kv_len, k_pages=k_pages, v_pages=v_pages, page_table=table,
                                    ring=ring, page_size=page, **common)

@@ -84,10 +84,13 @@ class GatedRecurrence(Part):
         kernels.causal_conv(x_raw, self.x_bias, self.conv, self.conv_bias, "none", ctx.tok_seq, ctx.positions, *seq,
                             self.tail_off, u)
         pre = torch.empty((T, 2 * W), dtype=torch.float32, device=x.device)
-        kernels.heads_linear(u, self.bs, self.w_gates, pre, 2 * self.bs)
+        if kernels.block_matvec_ok(T, self.bs):
+            kernels.block_matvec_f32(u, self.bs, self.w_gates, pre, 2 * self.bs)       # a handful of tokens: a stream of the matrices
+        else:
+            kernels.heads_linear(u, self.bs, self.w_gates, pre, 2 * self.bs)
         out = torch.empty((T, W), dtype=ctx.dtype, device=x.device)
         kernels.gated_scan(pre, u, proj[:, :W], self.y_bias, self.r_bias, self.i_bias, self.lam, self.decay_scale,
-                           self.bs, *seq, out, ctx.batch)
+                           self.bs, ctx.positions, *seq, out, ctx.batch, ctx.max_q_len)
         kernels.conv_tail(x_raw, self.x_bias, self.taps, *seq, self.tail_off, ctx.batch)
         return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
 

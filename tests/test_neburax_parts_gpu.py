@@ -208,9 +208,9 @@ def test_gated_scan_remembers_for_thousands_of_tokens():
         state = torch.zeros(2, W, device=DEV)
         out = torch.empty(T, W, device=DEV)
         args = lambda lo, hi: (pre[lo:hi].to(DEV), u[lo:hi].to(DEV), y_raw[lo:hi].to(DEV), None, zeros, zeros, lam.to(DEV), 8.0, W)
-        kernels.gated_scan(*args(0, cut), i32([0, cut]), i32([cut]), i32([0]), state, out[:cut], 1)
+        kernels.gated_scan(*args(0, cut), i32(list(range(cut))), i32([0, cut]), i32([cut]), i32([0]), state, out[:cut], 1, cut)
         for t in range(cut, T):
-            kernels.gated_scan(*args(t, t + 1), i32([0, 1]), i32([t + 1]), i32([0]), state, out[t:t + 1], 1)
+            kernels.gated_scan(*args(t, t + 1), i32([t]), i32([0, 1]), i32([t + 1]), i32([0]), state, out[t:t + 1], 1, 1)
             if cut == 2000 and t > 2040:
                 out[t + 1:] = ref[t + 1:].float().to(DEV)
                 break
