@@ -375,7 +375,8 @@ def neburax_main(args, pk) -> int:
     nh, P, N, grp = z["ssm_heads"], z["ssm_vdim"], z["state"], z["groups"]
     inner, cols = nh * P, nh * P + 2 * grp * N
     tf, gb = pk["bf16_burst"] * 1e12, pk["hbm_gbs"] * 1e9
-    active = min(z["experts"], batch * top)
+    # experts that a step of `batch` tokens is expected to touch (uniform choices; identity choices touch none)
+    active = z["experts"] * (1.0 - (1.0 - top / (z["experts"] + z["identity"])) ** batch)
     n_pair, n_ssm, n_moe = 2, 2, 3
     # (kernel-name fragment, work of all its launches in one pass over the layers, bound)
     rows = [

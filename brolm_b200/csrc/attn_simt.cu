@@ -54,6 +54,7 @@ struct AttnArgs {
     float scale, cap;
     int window;
     int chunk;                // > 0: keys before the start of the query's chunk are not visible
+    int vec;                  // rows are read eight elements at a time (sizes and strides allow it); else one by one
     const float* sink;        // [n_kv * group] or null: exp(sink[head]) joins the softmax's denominator, with no value
 };
 
@@ -62,7 +63,8 @@ template <typename T, int DPL, bool PAGED>
 __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
     extern __shared__ __align__(16) float smem[];
     const int hd = a.hd, vd = a.vd;
-    const int qs = hd + 4;                 // padded stride of q and k rows (floats)
+    const int hd4 = (hd + 3) & ~3;         // rows of q and k are padded with zeros to a multiple of four
+    const int qs = hd4 + 4;                // padded stride of q and k rows (floats)
     float* Qs = smem;                      // [ROWS][qs]
     float* Ks = Qs + ROWS * qs;            // [KT][qs]
     float* Vs = Ks + KT * qs;              // [KT][vd]
@@ -80,7 +82,18 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
 
     // stage the queries of this tile as floats
     const T* qg = (const T*)a.q;
-    for (int idx = threadIdx.x; idx < ROWS * (hd / 8); idx += blockDim.x) {
+    if (!a.vec) {
+        for (int idx = threadIdx.x; idx < ROWS * hd4; idx += blockDim.x) {
+            const int r = idx / hd4, c = idx - r * hd4;
+            float v = 0.0f;
+            if (r < rows_here && c < hd) {
+                const int row = row0 + r, tok = row / a.group, head = g * a.group + row % a.group;
+                v = to_float(qg[(size_t)(q0 + tok) * a.q_stride + head * hd + c]);
+            }
+            Qs[r * qs + c] = v;
+        }
+    }
+    for (int idx = threadIdx.x; a.vec && idx < ROWS * (hd / 8); idx += blockDim.x) {
         const int r = idx / (hd / 8), c = (idx - r * (hd / 8)) * 8;
         float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         if (r < rows_here) {
@@ -114,7 +127,39 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
     for (int t0 = (key_lo / KT) * KT; t0 <= key_hi; t0 += KT) {
         __syncthreads();   // the tile before this one is consumed (and Qs is written, first time)
         // stage keys and values t0 .. t0+KT-1; places outside [key_lo, key_hi] read as zero
-        for (int idx = threadIdx.x; idx < KT * (hd / 8); idx += blockDim.x) {
+        if (!a.vec) {
+            for (int idx = threadIdx.x; idx < KT * hd4; idx += blockDim.x) {
+                const int j = idx / hd4, c = idx - j * hd4;
+                const int kp = t0 + j;
+                float v = 0.0f;
+                if (kp >= key_lo && kp <= key_hi && c < hd) {
+                    if (PAGED) {
+                        const int ridx = kp % a.ring;
+                        const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
+                        v = to_float(((const T*)a.k_pages)[(((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * hd + c]);
+                    } else {
+                        v = to_float(((const T*)a.k)[(size_t)(q0 + kp) * a.kv_stride + g * hd + c]);
+                    }
+                }
+                Ks[j * qs + c] = v;
+            }
+            for (int idx = threadIdx.x; idx < KT * vd; idx += blockDim.x) {
+                const int j = idx / vd, c = idx - j * vd;
+                const int kp = t0 + j;
+                float v = 0.0f;
+                if (kp >= key_lo && kp <= key_hi) {
+                    if (PAGED) {
+                        const int ridx = kp % a.ring;
+                        const int page = a.page_table[(size_t)b * a.pt_stride + ridx / a.page_size];
+                        v = to_float(((const T*)a.v_pages)[(((size_t)page * a.n_kv + g) * a.page_size + ridx % a.page_size) * vd + c]);
+                    } else {
+                        v = to_float(((const T*)a.v)[(size_t)(q0 + kp) * a.v_stride + g * vd + c]);
+                    }
+                }
+                Vs[j * vd + c] = v;
+            }
+        }
+        for (int idx = threadIdx.x; a.vec && idx < KT * (hd / 8); idx += blockDim.x) {
             const int j = idx / (hd / 8), c = (idx - j * (hd / 8)) * 8;
             const int kp = t0 + j;
             float kv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -131,7 +176,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) Ks[j * qs + c + i] = kv[i];
         }
-        for (int idx = threadIdx.x; idx < KT * (vd / 8); idx += blockDim.x) {
+        for (int idx = threadIdx.x; a.vec && idx < KT * (vd / 8); idx += blockDim.x) {
             const int j = idx / (vd / 8), c = (idx - j * (vd / 8)) * 8;
             const int kp = t0 + j;
             float vv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -155,7 +200,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
 #pragma unroll
         for (int i = 0; i < RPW; ++i) s[i] = 0.0f;
         const float* kr = Ks + lane * qs;
-        for (int c = 0; c < hd; c += 4) {
+        for (int c = 0; c < hd4; c += 4) {
             const float4 kk = *reinterpret_cast<const float4*>(kr + c);
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
@@ -223,7 +268,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_simt_kernel(AttnArgs a) {
 
 template <typename T, int DPL>
 int launch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream_t stream) {
-    const size_t smem = (size_t)((ROWS + KT) * (a.hd + 4) + KT * a.vd) * sizeof(float);
+    const size_t smem = (size_t)((ROWS + KT) * (((a.hd + 3) & ~3) + 4) + KT * a.vd) * sizeof(float);
     if (smem > 227 * 1024) return BROLM_ERR_TOO_LARGE;
     dim3 grid((max_q_len * a.group + ROWS - 1) / ROWS, a.n_kv, batch);
     static size_t allowed[2] = {0, 0};        // raised once per size, not at every launch
@@ -255,29 +300,30 @@ int dispatch(const AttnArgs& a, bool paged, int batch, int max_q_len, cudaStream
 
 }  // namespace
 
-// head_dim must be a multiple of 8 and at most 512; strides and the offsets of
-// heads must keep 8 elements in one aligned 16-byte (bf16) or 32-byte (float)
-// span, which holds when every stride is a multiple of 8.
+// head_dim and the value size are at most 512.  Rows are read eight elements at a time when both are
+// multiples of 8 and every stride is a multiple of 8 (8 elements then lie in one aligned 16-byte (bf16) or
+// 32-byte (float) span); other sizes and strides are read one element at a time.
 BROLM_API int brolm_attn_simt(int dtype, const void* q, int q_stride, void* out, int out_stride, const void* cu_q,
                               const void* kv_len, const void* k, const void* v, int kv_stride, const void* k_pages,
                               const void* v_pages, const void* page_table, int pt_stride, int ring, int page_size,
                               int n_kv, int group, int hd, float scale, float cap, int window, const void* sink,
                               int batch, int max_q_len, int vd, int v_stride, int chunk, cudaStream_t stream) {
     if (batch <= 0 || max_q_len <= 0) return BROLM_OK;
-    if (hd <= 0 || hd % 8 != 0 || hd > 512 || group <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
-    if (vd <= 0 || vd % 8 != 0 || vd > 512) return BROLM_ERR_BAD_SIZE;
-    if (q_stride % 8 != 0 || out_stride % 8 != 0) return BROLM_ERR_ALIGNMENT;
+    if (hd <= 0 || hd > 512 || group <= 0 || n_kv <= 0) return BROLM_ERR_BAD_SIZE;
+    if (vd <= 0 || vd > 512) return BROLM_ERR_BAD_SIZE;
+    bool vec = hd % 8 == 0 && vd % 8 == 0 && q_stride % 8 == 0 && ((uintptr_t)q & 15) == 0;
     if (batch > 65535 || n_kv > 65535) return BROLM_ERR_TOO_LARGE;
     const bool paged = k_pages != nullptr;
     if (paged) {
         if (ring <= 0 || page_size <= 0 || page_size % KT != 0 || ring % page_size != 0) return BROLM_ERR_BAD_SIZE;
     } else {
-        if (!k || !v || kv_stride % 8 != 0 || v_stride % 8 != 0) return BROLM_ERR_ALIGNMENT;
+        if (!k || !v) return BROLM_ERR_ALIGNMENT;
+        vec = vec && kv_stride % 8 == 0 && v_stride % 8 == 0 && ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0;
     }
     AttnArgs a;
     a.q = q; a.out = out; a.q_stride = q_stride; a.out_stride = out_stride;
     a.cu_q = (const int32_t*)cu_q; a.kv_len = (const int32_t*)kv_len;
-    a.k = k; a.v = v; a.kv_stride = kv_stride; a.v_stride = v_stride; a.vd = vd; a.chunk = chunk;
+    a.k = k; a.v = v; a.kv_stride = kv_stride; a.v_stride = v_stride; a.vd = vd; a.chunk = chunk; a.vec = vec ? 1 : 0;
     a.k_pages = k_pages; a.v_pages = v_pages; a.page_table = (const int32_t*)page_table;
     a.pt_stride = pt_stride; a.ring = ring; a.page_size = page_size;
     a.n_kv = n_kv; a.group = group; a.hd = hd; a.scale = scale; a.cap = cap; a.window = window; a.sink = (const float*)sink;

@@ -39,9 +39,8 @@ class Attention(Part):
         if n_q % n_kv:
             raise ValueError("attention: the number of query heads must be a multiple of the kv heads")
         plain = not (v_dim and v_dim != head_dim) and qk_norm == "none" and not chunk
-        if head_dim % (16 if plain else 8):
-            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of {16 if plain else 8}; the kernels "
-                             f"refuse it")
+        if plain and head_dim % 16:
+            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of 16; the kernels refuse it")
         if head_dim > 512:
             raise ValueError(f"attention: head_dim {head_dim} is beyond the kernels' limit of 512")
         if qk_norm not in ("none", "whole"):
@@ -57,8 +56,8 @@ class Attention(Part):
         # the options of the second paragraph above: their own row-wise kernel and the exact attention
         self.rowwise = self.v_dim != head_dim or qk_norm != "none" or self.chunk is not None
         if self.rowwise:
-            if self.v_dim % 8 or self.v_dim > 512 or head_dim % 8:
-                raise ValueError(f"attention: v_dim {self.v_dim} must be a multiple of 8 of at most 512")
+            if self.v_dim > 512:
+                raise ValueError(f"attention: v_dim {self.v_dim} is beyond the kernels' limit of 512")
             if position is not None:
                 raise ValueError("attention: a rotation together with v_dim, qk_norm or chunk is not built")
 

@@ -43,13 +43,13 @@ CFG_S = dict(
             ssm(2, 24, 12, 1, 3, 5)])
 
 # T: real routing (2 of 5 + 2 identity, 1 of 4), a chunk of one page exactly (64) and one across a page border (70),
-# as many key heads as query heads, key and value heads of one size, one block, a convolution of one tap (no kept
+# as many key heads as query heads, key and value heads of one size, head sizes that are no multiples of 8, one block, a convolution of one tap (no kept
 # inputs), no shared expert, no identity experts, sizes that are no multiples of 16.
 CFG_T = dict(
     architecture="Neburax", vocab=50, width=40, norm=dict(eps=1e-6),
     layers=[ssm(5, 8, 40, 5, 5, 3, mlp=moe(20, 5, 2, identity=2)),
             pair(3, 3, 24, 24, 0.2, 64, 40, 1, 1, 1.0, 0.5, mlp=moe(36, 4, 1)),
-            pair(6, 1, 16, 8, 0.25, 70, 24, 3, 2, 1.5, 1.0, mlp=dense(56))])
+            pair(6, 1, 12, 6, 0.25, 70, 24, 3, 2, 1.5, 1.0, mlp=dense(56))])
 
 # U: one layer run three times, each run with a state of its own; a chunk of one (a token sees itself alone) and,
 # in the other layer, a chunk longer than any prompt of the tests; a router with identity experts only.

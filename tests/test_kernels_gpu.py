@@ -741,10 +741,10 @@ def test_attention_prompt_and_decode_agree_bitwise():
 
 
 def test_kernels_refuse_what_they_cannot_do():
-    q = torch.zeros(2, 24, device=DEV)
-    with pytest.raises(kernels.KernelError):
+    q = torch.zeros(2, 2 * 520, device=DEV)
+    with pytest.raises(kernels.KernelError):                # a head beyond the exact kernel's 512
         kernels.attention_simt(q, torch.empty_like(q), torch.tensor([0, 2], dtype=torch.int32, device=DEV),
-                               torch.tensor([2], dtype=torch.int32, device=DEV), n_kv=1, group=2, head_dim=12,
+                               torch.tensor([2], dtype=torch.int32, device=DEV), n_kv=1, group=2, head_dim=520,
                                scale=1.0, cap=0.0, window=0, batch=1, max_q_len=2, k=q, v=q)
     with pytest.raises(kernels.KernelError):
         kernels.gated_act(torch.zeros(1, 8, device=DEV), torch.zeros(1, 4, device=DEV), "relu")

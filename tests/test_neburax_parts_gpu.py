@@ -66,7 +66,7 @@ def chunk_ref(q, k, v, H, G, d, dv, scale, chunk):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,dv,chunk,n", [(4, 2, 8, 16, 9, 40), (3, 3, 24, 24, 64, 200), (6, 1, 16, 8, 70, 200),
+@pytest.mark.parametrize("H,G,d,dv,chunk,n", [(4, 2, 8, 16, 9, 40), (3, 3, 24, 24, 64, 200), (6, 1, 12, 6, 70, 200), (5, 5, 10, 14, 33, 100),
                                              (2, 1, 16, 32, 1, 20), (4, 2, 64, 128, 512, 700), (8, 2, 32, 8, 128, 300)])
 def test_chunked_attention_kernel_with_one_key_that_carries_the_weight(dtype, H, G, d, dv, chunk, n):
     """The key at a chunk's first place carries the weight for the chunk's last query (hundreds of places back when
@@ -114,7 +114,7 @@ def test_chunked_attention_kernel_with_one_key_that_carries_the_weight(dtype, H,
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,dv,chunk", [(4, 2, 8, 16, 9), (3, 3, 24, 24, 64), (6, 1, 16, 8, 70), (2, 1, 16, 32, 1)])
+@pytest.mark.parametrize("H,G,d,dv,chunk", [(4, 2, 8, 16, 9), (3, 3, 24, 24, 64), (6, 1, 12, 6, 70), (5, 5, 10, 14, 33), (2, 1, 16, 32, 1)])
 def test_attention_part_with_whole_row_norm_prompt_then_decode(dtype, H, G, d, dv, chunk):
     hidden, eps, scale = 40, 1e-5, 0.3
     att = Attention(hidden, H, G, d, scale, v_dim=dv, qk_norm="whole", eps=eps, chunk=chunk)
