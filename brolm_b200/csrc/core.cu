@@ -293,7 +293,12 @@ __global__ void __launch_bounds__(256, (MAXC >= 1 && MAXC <= 3) ? 4 : 1) residua
             hr[i] = s;
             ss2 += s * s;
         }
-        if (!w_next) return;
+        if (!w_next) {
+            // no norm for the block that follows: the new stream itself in its element type, if asked for
+            if (out)
+                for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<O>(hr[i]);
+            return;
+        }
         ss2 = block_sum(ss2, scratch);
         const float inv_next = rsqrtf(ss2 / (float)hidden + eps_next);
         // every thread reads back only what it wrote itself
@@ -361,7 +366,10 @@ __global__ void __launch_bounds__(256, (MAXC >= 1 && MAXC <= 3) ? 4 : 1) residua
             res[c][e] += v[c][e];
             ss2 += res[c][e] * res[c][e];
         }
-        if (i < hidden) store4(hr + i, res[c]);
+        if (i < hidden) {
+            store4(hr + i, res[c]);
+            if (!w_next && out) store4(dst + i, res[c]);
+        }
     }
     if (!w_next) return;
     ss2 = block_sum_once(ss2, scratch, 1);
@@ -459,6 +467,7 @@ __global__ void __launch_bounds__(256, 8) residual_rmsnorm_rows_kernel(float* __
         if (i < hidden) {
             store4(hr + i, res);
             if (w_next) store4(sh + i, res);
+            else if (out) store4(dst + i, res);
         }
     }
     if (!w_next) return;
@@ -518,7 +527,8 @@ static int residual_out(void* h, const void* y, int n_parts, long long part_stri
     return BROLM_ERR_BAD_DTYPE;
 }
 
-// w_post and w_next share one element type (w_dtype); either may be null.
+// w_post and w_next share one element type (w_dtype); either may be null.  With w_next null and out given, out takes
+// the new stream itself in out's element type (for a block that reads the stream without a norm).
 BROLM_API int brolm_residual_rmsnorm(void* h, const void* y, int y_dtype, int n_parts, long long part_stride,
                                      const void* w_post, float eps_post,
                                      float off_post, const void* w_next, float eps_next, float off_next,

@@ -133,7 +133,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, ou
 def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[torch.Tensor], post_eps: float,
                      post_offset: float, next_weight: Optional[torch.Tensor], next_eps: float, next_offset: float,
                      out: Optional[torch.Tensor]) -> None:
-    """h += rmsnorm(y; post) (or y when post_weight is None); out = rmsnorm(h; next) when next_weight is given.
+    """h += rmsnorm(y; post) (or y when post_weight is None); out = rmsnorm(h; next) when next_weight is given;
+    with ``out`` but no ``next_weight``, out = the new h in out's element type.
 
     ``y`` may be [parts, rows, hidden]: partial sums that are added in order first."""
     assert h.dtype == torch.float32 and h.is_contiguous() and y.is_contiguous() and tuple(y.shape[-2:]) == tuple(h.shape)
@@ -146,13 +147,15 @@ def residual_rmsnorm(h: torch.Tensor, y: torch.Tensor, post_weight: Optional[tor
                 raise KernelError("residual_rmsnorm: both gains must have one element type")
             wd = w.dtype
     if next_weight is not None:
-        assert out is not None and out.is_contiguous() and out.shape == h.shape
+        assert out is not None
+    if out is not None:
+        assert out.is_contiguous() and out.shape == h.shape
     f = _fn("core", "brolm_residual_rmsnorm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float, c_float,
                                                c_void_p, c_float, c_float, c_int, c_void_p, c_int, c_int, c_int,
                                                c_void_p])
     _check(f(_ptr(h), _ptr(y), _code(y), n_parts, part_stride, _ptr(post_weight), post_eps, post_offset, _ptr(next_weight), next_eps,
-             next_offset, _CODES[wd] if wd is not None else F32, _ptr(out) if next_weight is not None else None,
-             _code(out) if next_weight is not None else F32, h.shape[0], h.shape[-1], _stream()),
+             next_offset, _CODES[wd] if wd is not None else F32, _ptr(out) if out is not None else None,
+             _code(out) if out is not None else F32, h.shape[0], h.shape[-1], _stream()),
            "residual_rmsnorm")
 
 

@@ -73,8 +73,10 @@ def add_then_norm(h: torch.Tensor, y: torch.Tensor, post: Optional[Part], nxt: O
     own ``apply`` and only the sum stays fused.
     """
     fused_post = post is None or isinstance(post, RMSNorm)
-    fused_next = nxt is None or isinstance(nxt, RMSNorm)
-    if fused_post and fused_next and post is not None and nxt is not None and post.weight.dtype != nxt.weight.dtype:
+    plain_next = isinstance(nxt, Cast)          # no norm ahead of the next block: it wants the stream itself
+    fused_next = nxt is None or plain_next or isinstance(nxt, RMSNorm)
+    if fused_post and fused_next and post is not None and nxt is not None and not plain_next \
+            and post.weight.dtype != nxt.weight.dtype:
         fused_next = False
     if y.dim() == 3 and not fused_post:
         y = y.sum(dim=0)                       # partial sums, and a norm that wants the whole
@@ -82,14 +84,17 @@ def add_then_norm(h: torch.Tensor, y: torch.Tensor, post: Optional[Part], nxt: O
         y = post.apply(y, torch.float32)
         post = None
     out = None
-    if fused_next and nxt is not None:
+    if fused_next and nxt is not None and not (plain_next and out_dtype == torch.float32):
         out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+    normed_next = fused_next and nxt is not None and not plain_next
     kernels.residual_rmsnorm(
         h, y,
         post.weight if post is not None else None, post.eps if post is not None else 0.0,
         post.offset if post is not None else 0.0,
-        nxt.weight if (fused_next and nxt is not None) else None, nxt.eps if (fused_next and nxt is not None) else 0.0,
-        nxt.offset if (fused_next and nxt is not None) else 0.0, out)
+        nxt.weight if normed_next else None, nxt.eps if normed_next else 0.0,
+        nxt.offset if normed_next else 0.0, out)
+    if plain_next and out is None:
+        return h                               # float32: the stream is handed on as it is
     if nxt is not None and not fused_next:
         out = nxt.apply(h, out_dtype)
     return out
