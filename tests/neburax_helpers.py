@@ -52,14 +52,16 @@ CFG_T = dict(
             pair(6, 1, 12, 6, 0.25, 70, 24, 3, 2, 1.5, 1.0, mlp=dense(56))])
 
 # U: one layer run three times, each run with a state of its own; a chunk of one (a token sees itself alone) and,
-# in the other layer, a chunk longer than any prompt of the tests; a router with identity experts only.
+# in another layer, a chunk longer than any prompt of the tests; a router with identity experts only; two layers whose
+# key and value heads have one size that is a multiple of 16 (in bfloat16 their attention runs on the tensor cores).
 CFG_U = dict(
     architecture="Neburax", vocab=64, width=32, norm=dict(eps=1e-5),
     layers=[pair(2, 1, 16, 32, 0.35, 1, 16, 4, 3, 0.9, 1.1, mlp=moe(16, 0, 2, identity=2, shared=24)),
             pair(2, 1, 16, 32, 0.35, 1, 16, 4, 3, 0.9, 1.1, mlp=moe(16, 0, 2, identity=2, shared=24), weights_of=0),
             ssm(1, 32, 64, 1, 2, 4, mlp=dense(16)),
             pair(2, 1, 16, 32, 0.35, 1, 16, 4, 3, 0.9, 1.1, mlp=moe(16, 0, 2, identity=2, shared=24), weights_of=0),
-            pair(4, 2, 8, 8, 0.5, 1000, 48, 2, 2, 1.0, 1.0)])
+            pair(4, 2, 16, 16, 0.5, 1000, 48, 2, 2, 1.0, 1.0),
+            pair(2, 2, 32, 32, 0.3, 40, 32, 2, 2, 1.0, 1.0, mlp=dense(24))])
 
 CONFIGS = {"S": (CFG_S, 3, 0.15), "T": (CFG_T, 4, 0.2), "U": (CFG_U, 5, 0.2)}      # name -> (config, seed, weight std)
 

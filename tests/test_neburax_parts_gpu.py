@@ -114,7 +114,10 @@ def test_chunked_attention_kernel_with_one_key_that_carries_the_weight(dtype, H,
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,d,dv,chunk", [(4, 2, 8, 16, 9), (3, 3, 24, 24, 64), (6, 1, 12, 6, 70), (5, 5, 10, 14, 33), (2, 1, 16, 32, 1)])
+@pytest.mark.parametrize("H,G,d,dv,chunk", [(4, 2, 8, 16, 9), (3, 3, 24, 24, 64), (6, 1, 12, 6, 70), (5, 5, 10, 14, 33), (2, 1, 16, 32, 1),
+                                            # key and value rows of one size, a multiple of 16: in bfloat16 the tensor-core kernels
+                                            (4, 2, 32, 32, 9), (2, 1, 64, 64, 70), (2, 2, 128, 128, 100), (4, 1, 16, 16, 1),
+                                            (2, 1, 48, 48, 33), (8, 2, 64, 64, 64), (2, 1, 32, 32, 1000)])
 def test_attention_part_with_whole_row_norm_prompt_then_decode(dtype, H, G, d, dv, chunk):
     hidden, eps, scale = 40, 1e-5, 0.3
     att = Attention(hidden, H, G, d, scale, v_dim=dv, qk_norm="whole", eps=eps, chunk=chunk)
