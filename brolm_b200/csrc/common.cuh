@@ -154,6 +154,19 @@ static inline bool pdl_enabled() {
     return on == 1;
 }
 
+// The same launch in plain stream order: for a kernel that runs long on few warps per SM.  Let in early, its blocks
+// land wherever the kernel before it leaves room, several on one SM and none on another, and stay that way to the end.
+template <typename... KArgs, typename... Args>
+static inline int launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                              Args... args) {

@@ -69,6 +69,66 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const X* __restrict__ 
     out[(size_t)t * ldo + c] = acc;
 }
 
+// The same for up to CONV_KMAX taps with a thread taking a run of CONV_RUN packed tokens of one channel: the taps'
+// inputs slide through registers (newest last, unused places weigh zero), so a token of the same sequence as the one
+// before it costs one load instead of K.
+constexpr int CONV_KMAX = 8, CONV_RUN = 8;
+
+template <typename X>
+__global__ void __launch_bounds__(256) causal_conv_run_kernel(const X* __restrict__ x, long ldx, const float* __restrict__ in_bias,
+                                                              const float* __restrict__ w, const float* __restrict__ bias, int C,
+                                                              int K, int act, const int32_t* __restrict__ tok_seq,
+                                                              const int32_t* __restrict__ positions, SeqArgs s, long tail_off,
+                                                              float* __restrict__ out, long ldo, int tokens) {
+    pdl_trigger();
+    const int t0 = blockIdx.x * CONV_RUN;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float wr[CONV_KMAX], win[CONV_KMAX];
+#pragma unroll
+    for (int jj = 0; jj < CONV_KMAX; ++jj) {
+        const int j = jj - (CONV_KMAX - K);
+        wr[jj] = j >= 0 ? w[(size_t)c * K + j] : 0.0f;
+        win[jj] = 0.0f;
+    }
+    const float ib = in_bias ? in_bias[c] : 0.0f, bo = bias ? bias[c] : 0.0f;
+    pdl_wait();
+    int prev_b = -1, prev_pos = -2;
+    for (int i = 0; i < CONV_RUN && t0 + i < tokens; ++i) {
+        const int t = t0 + i;
+        const int pos = positions[t];
+        if (pos < 0) { prev_b = -1; continue; }
+        const int b = tok_seq[t];
+        if (b == prev_b && pos == prev_pos + 1) {
+#pragma unroll
+            for (int jj = 0; jj < CONV_KMAX - 1; ++jj) win[jj] = win[jj + 1];
+            win[CONV_KMAX - 1] = to_float(x[(size_t)t * ldx + c]) + ib;
+        } else {
+            const int q0 = s.cu_q[b], q_len = s.cu_q[b + 1] - q0;
+            const int first = s.kv_len[b] - q_len;
+            const float* tail = s.state + (size_t)s.slots[b] * s.state_stride + tail_off;
+#pragma unroll
+            for (int jj = 0; jj < CONV_KMAX; ++jj) {
+                const int j = jj - (CONV_KMAX - K);
+                float v = 0.0f;
+                if (j >= 0) {
+                    const int q = pos - (K - 1) + j;
+                    v = q >= first ? to_float(x[(size_t)(q0 + q - first) * ldx + c]) + ib
+                                   : tail[(size_t)(q - first + K - 1) * C + c];
+                }
+                win[jj] = v;
+            }
+        }
+        prev_b = b;
+        prev_pos = pos;
+        float acc = bo;
+#pragma unroll
+        for (int jj = 0; jj < CONV_KMAX; ++jj) acc = fmaf(wr[jj], win[jj], acc);
+        if (act == CONV_SILU) acc = acc / (1.0f + expf(-acc));
+        out[(size_t)t * ldo + c] = acc;
+    }
+}
+
 // tail[k][c] <- in(new_len - (K-1) + k, c), k = 0 .. K-2, ascending: place k reads old place k + q_len, which
 // is written later.
 template <typename X>
@@ -135,7 +195,9 @@ __global__ void __launch_bounds__(GS_CH * NSEG) gated_scan_kernel(const float* _
                                                                   long ldy, const float* __restrict__ yb, int width, int bs,
                                                                   SeqArgs s, O* __restrict__ out, long ldo) {
     __shared__ float seg_sum[NSEG][GS_CH], seg_end[NSEG][GS_CH];
-    pdl_trigger();
+    // A prompt's scan runs long on few warps: it is launched in plain stream order and lets nothing in early; only the
+    // short form for single tokens takes part in programmatic launch.
+    if (NSEG == 1) pdl_trigger();
     const int b = blockIdx.y, cl = threadIdx.x, seg = threadIdx.y;
     const int c = blockIdx.x * GS_CH + cl;
     const int kv_len = s.kv_len[b];
@@ -229,13 +291,18 @@ __device__ __forceinline__ void cp_async16f(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-template <typename X, int NPT, int PT>
+template <typename X, int NPT, int PT, int NS>       // NS: the lanes per tile when known at compile time, else 0
 __global__ void __launch_bounds__(128) ssm_scan_kernel(const float* __restrict__ xbc, long ldx, const X* __restrict__ dt_raw, long lddt,
                                                        const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                                                        const float* __restrict__ Dv, int heads, int groups, int P, int N,
-                                                       int nsplit, int vec, SeqArgs s, float* __restrict__ y, long ldy) {
+                                                       int nsplit_rt, int vec, int early, SeqArgs s, float* __restrict__ y,
+                                                       long ldy) {
     extern __shared__ __align__(16) float sm[];
-    pdl_trigger();
+    // A prompt's scan runs long on one or two warps a scheduler: it is launched in plain stream order (let in early, its
+    // blocks land unevenly on the SMs and it takes 0.93 instead of 0.48 ms) and lets nothing in early; only a step of
+    // single tokens takes part in programmatic launch.
+    if (early) pdl_trigger();
+    const int nsplit = NS > 0 ? NS : nsplit_rt;
     const int VP = (128 / nsplit) * PT, NP = nsplit * NPT;            // values of p a block takes; padded N
     const int stage_floats = 2 * SSM_TC * NP + SSM_TC * VP + SSM_TC;   // B, C, x, raw dt
     float* sdt = sm + 2 * stage_floats;     // [TC]
@@ -440,6 +507,18 @@ BROLM_API int brolm_causal_conv(const void* x, int x_dtype, long ldx, const void
     if (C <= 0 || K <= 0 || (act != CONV_NONE && act != CONV_SILU)) return BROLM_ERR_BAD_SIZE;
     if ((C + 255) / 256 > 65535) return BROLM_ERR_TOO_LARGE;
     const SeqArgs s = seq_args(cu_q, kv_len, slots, state, state_stride);
+    if (K <= CONV_KMAX && tokens > 64) {       // a prompt: runs of tokens per thread
+        dim3 rgrid((tokens + CONV_RUN - 1) / CONV_RUN, (C + 255) / 256);
+        if (x_dtype == BROLM_F32)
+            return launch_pdl(causal_conv_run_kernel<float>, rgrid, dim3(256), 0, stream, (const float*)x, ldx,
+                              (const float*)in_bias, (const float*)w, (const float*)bias, C, K, act, (const int32_t*)tok_seq,
+                              (const int32_t*)positions, s, tail_off, (float*)out, ldo, tokens);
+        if (x_dtype == BROLM_BF16)
+            return launch_pdl(causal_conv_run_kernel<bf16>, rgrid, dim3(256), 0, stream, (const bf16*)x, ldx,
+                              (const float*)in_bias, (const float*)w, (const float*)bias, C, K, act, (const int32_t*)tok_seq,
+                              (const int32_t*)positions, s, tail_off, (float*)out, ldo, tokens);
+        return BROLM_ERR_BAD_DTYPE;
+    }
     dim3 grid(tokens, (C + 255) / 256);
     if (x_dtype == BROLM_F32)
         return launch_pdl(causal_conv_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ldx, (const float*)in_bias,
@@ -489,7 +568,7 @@ BROLM_API int brolm_gated_scan(void* pre, long ldpre, const void* u, long ldu, c
 #define BROLM_GS(Y, O)                                                                                                          \
     do {                                                                                                                        \
         if (max_q_len > 32)                                                                                                     \
-            return launch_pdl(gated_scan_kernel<Y, O, 32>, grid, dim3(GS_CH, 32), 0, stream, (const float*)pre, ldpre,            \
+            return launch_in_order(gated_scan_kernel<Y, O, 32>, grid, dim3(GS_CH, 32), 0, stream, (const float*)pre, ldpre,       \
                               (const Y*)y_raw, ldy, (const float*)yb, width, bs, s, (O*)out, ldo);                              \
         return launch_pdl(gated_scan_kernel<Y, O, 1>, grid, dim3(GS_CH, 1), 0, stream, (const float*)pre, ldpre,                \
                           (const Y*)y_raw, ldy, (const float*)yb, width, bs, s, (O*)out, ldo);                                  \
@@ -505,7 +584,7 @@ BROLM_API int brolm_gated_scan(void* pre, long ldpre, const void* u, long ldu, c
 BROLM_API int brolm_ssm_scan(const void* xbc, long ldx, const void* dt_raw, int dt_dtype, long lddt, const void* dt_bias,
                              const void* A_log, const void* Dv, int heads, int groups, int P, int N, const void* cu_q,
                              const void* kv_len, const void* slots, void* state, long state_stride, void* y, long ldy,
-                             int batch, cudaStream_t stream) {
+                             int batch, int max_q_len, cudaStream_t stream) {
     if (batch <= 0) return BROLM_OK;
     if (heads <= 0 || groups <= 0 || heads % groups || P <= 0 || N <= 0) return BROLM_ERR_BAD_SIZE;
     if (N > 256 || batch > 65535 || heads > 65535) return BROLM_ERR_TOO_LARGE;
@@ -520,30 +599,43 @@ BROLM_API int brolm_ssm_scan(const void* xbc, long ldx, const void* dt_raw, int 
         }
     // values of p per thread: four, unless that leaves the device with less than one warp per scheduler (one long
     // sequence alone: the loop over its tokens is a chain of dependent steps that only more warps can fill)
+    const int early = max_q_len <= 32 ? 1 : 0;
     int pt = 4;
     while (pt > 1 && (long long)batch * heads * ((P + pt - 1) / pt) * nsplit < 1LL * 4 * 32 * device_sm_count()) pt >>= 1;
+    if (const char* e = getenv("BROLM_SSM_PT")) {          // (for measurements)
+        const int want = atoi(e);
+        if (want == 1 || want == 2 || want == 4) pt = want;
+    }
     const int VP = (128 / nsplit) * pt;
     const int vec = N % 4 == 0 && ldx % 4 == 0 && (heads * P) % 4 == 0 && ((uintptr_t)xbc & 15) == 0;
     const SeqArgs s = seq_args(cu_q, kv_len, slots, state, state_stride);
     dim3 grid((P + VP - 1) / VP, heads, batch);
     const size_t smem = (size_t)(2 * (2 * SSM_TC * nsplit * npt + SSM_TC * VP + SSM_TC) + 2 * SSM_TC) * sizeof(float);
-#define BROLM_SSM(NPT, PT)                                                                                                     \
+#define BROLM_SSM(NPT, PT, NS)                                                                                                 \
     do {                                                                                                                       \
         if (smem > 48 * 1024) {                                                                                                \
-            cudaError_t e = cudaFuncSetAttribute(ssm_scan_kernel<float, NPT, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                                 (int)smem);                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(ssm_scan_kernel<float, NPT, PT, NS>,                                          \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                      \
             if (e != cudaSuccess) return (int)e;                                                                               \
         }                                                                                                                      \
-        return launch_pdl(ssm_scan_kernel<float, NPT, PT>, grid, dim3(128), smem, stream, (const float*)xbc, ldx,              \
+        if (!early)                                                                                                            \
+            return launch_in_order(ssm_scan_kernel<float, NPT, PT, NS>, grid, dim3(128), smem, stream, (const float*)xbc, ldx, \
+                                   (const float*)dt_raw, lddt, (const float*)dt_bias, (const float*)A_log, (const float*)Dv,   \
+                                   heads, groups, P, N, nsplit, vec, early, s, (float*)y, ldy);                                \
+        return launch_pdl(ssm_scan_kernel<float, NPT, PT, NS>, grid, dim3(128), smem, stream, (const float*)xbc, ldx,          \
                           (const float*)dt_raw, lddt, (const float*)dt_bias, (const float*)A_log, (const float*)Dv, heads,     \
-                          groups, P, N, nsplit, vec, s, (float*)y, ldy);                                                       \
+                          groups, P, N, nsplit, vec, early, s, (float*)y, ldy);                                                \
     } while (0)
-#define BROLM_SSM_N(PT)                    \
-    do {                                   \
-        if (npt == 4) BROLM_SSM(4, PT);    \
-        if (npt == 8) BROLM_SSM(8, PT);    \
-        if (npt == 12) BROLM_SSM(12, PT);  \
-        BROLM_SSM(16, PT);                 \
+    // eight states per thread is what sizes of 64 states and more get: those know their lanes at compile time
+#define BROLM_SSM_N(PT)                                   \
+    do {                                                  \
+        if (npt == 4) BROLM_SSM(4, PT, 0);                \
+        if (npt == 8 && nsplit == 8) BROLM_SSM(8, PT, 8);   \
+        if (npt == 8 && nsplit == 16) BROLM_SSM(8, PT, 16); \
+        if (npt == 8 && nsplit == 32) BROLM_SSM(8, PT, 32); \
+        if (npt == 8) BROLM_SSM(8, PT, 0);                \
+        if (npt == 12) BROLM_SSM(12, PT, 0);              \
+        BROLM_SSM(16, PT, 0);                             \
     } while (0)
     if (dt_dtype != BROLM_F32) return BROLM_ERR_BAD_DTYPE;
     if (pt == 4) BROLM_SSM_N(4);

@@ -643,7 +643,7 @@ def block_matvec_f32(a: torch.Tensor, a_head: int, weight: torch.Tensor, out: to
 
 def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d: torch.Tensor,
              heads: int, groups: int, head_size: int, n_state: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
-             slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, batch: int) -> None:
+             slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, batch: int, max_q_len: int) -> None:
     """The selective state space over the packed tokens.  xbc float32 (tokens, heads * P + 2 * groups * N) =
     [x | B | C]; dt_raw (tokens, heads) may be a strided view; per head S (kept as [P][N] in ``state[slot]``):
     dt = softplus(dt_raw + dt_bias), S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d x."""
@@ -656,9 +656,10 @@ def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
         assert v.dtype == torch.float32 and v.is_contiguous() and v.numel() == heads
     f = _fn("recurrent", "brolm_ssm_scan", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_int,
                                             c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_void_p,
-                                            c_long, c_int, c_void_p])
+                                            c_long, c_int, c_int, c_void_p])
     _check(f(_ptr(xbc), xbc.stride(0), _ptr(dt_raw), _code(dt_raw), dt_raw.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(d),
-             heads, groups, P, N, *_seq(cu_q, kv_len, slots, state), _ptr(y), y.stride(0), batch, _stream()), "ssm_scan")
+             heads, groups, P, N, *_seq(cu_q, kv_len, slots, state), _ptr(y), y.stride(0), batch, max_q_len, _stream()),
+           "ssm_scan")
 
 
 def linear_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:

@@ -156,7 +156,7 @@ class StateSpace(Part):
                             self.tail_off, xbc)
         y = torch.empty((T, inner), dtype=torch.float32, device=x.device)
         kernels.ssm_scan(xbc, proj[:, inner + self.conv_cols:], self.dt_bias, self.a_log, self.d, self.heads, self.groups,
-                         self.P, self.N, *seq, y, ctx.batch)
+                         self.P, self.N, *seq, y, ctx.batch, ctx.max_q_len)
         kernels.conv_tail(raw, None, self.taps, *seq, self.tail_off, ctx.batch)
         out = torch.empty((T, inner), dtype=ctx.dtype, device=x.device)
         kernels.gate_group_norm(y, proj[:, :inner], self.gain, self.eps, self.norm_groups, out)

@@ -137,7 +137,7 @@ def test_attention_part_with_whole_row_norm_prompt_then_decode(dtype, H, G, d, d
 @pytest.mark.parametrize("C,K", [(5, 1), (40, 2), (300, 4), (33, 7)])
 def test_causal_convolution_prompt_then_tokens(C, K):
     g = torch.Generator().manual_seed(C)
-    lengths, extra = [1, 2, K + 3, 70], 2 * K + 1
+    lengths, extra = [1, 2, K + 3, 70], 2 * K + 1           # 76 tokens and more in the prompt step: a thread takes a run of tokens
     taps, bias, in_bias = torch.randn(C, K, generator=g), torch.randn(C, generator=g), torch.randn(C, generator=g)
     xs = [torch.randn(n + extra, C, generator=g) for n in lengths]
     refs = [plain.silu(plain.causal_conv(x.double() + in_bias.double(), taps.double(), bias.double())) for x in xs]
@@ -263,10 +263,10 @@ def test_state_space_scan_remembers_for_thousands_of_tokens():
         state = torch.zeros(2, heads * P * N, device=DEV)
         y = torch.empty(T, heads * P, device=DEV)
         consts = (dtb.to(DEV), a_log.to(DEV), d.to(DEV), heads, 1, P, N)
-        kernels.ssm_scan(xbc[:cut].to(DEV), dt_raw[:cut].to(DEV), *consts, i32([0, cut]), i32([cut]), i32([0]), state, y[:cut], 1)
+        kernels.ssm_scan(xbc[:cut].to(DEV), dt_raw[:cut].to(DEV), *consts, i32([0, cut]), i32([cut]), i32([0]), state, y[:cut], 1, cut)
         for t in range(cut, T):
             kernels.ssm_scan(xbc[t:t + 1].to(DEV), dt_raw[t:t + 1].to(DEV), *consts, i32([0, 1]), i32([t + 1]), i32([0]), state,
-                             y[t:t + 1], 1)
+                             y[t:t + 1], 1, 1)
         assert rel(y, ref) <= 2e-5, cut
 
 
