@@ -169,7 +169,24 @@ __global__ void __launch_bounds__(256) conv_tail_kernel(const X* __restrict__ x,
 // S -> exp(sum of its log a) S + its own end state), and scanned once more from their true beginnings for the
 // results.  One token per sequence (decoding) is one run.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) gate_prep_kernel(float* __restrict__ pre, long ldpre, const float* __restrict__ u, long ldu,
+// split_halves: u (float) -> [u_hi; u_lo] as bfloat16 rows, u_hi = bf16(u), u_lo = bf16(u - u_hi): together 16 bits of
+// u's mantissa.  With bfloat16 matrices the two products are exact in float, so W u_hi + W u_lo is the float product
+// of W with u cut to 16 bits, on the tensor cores.
+__global__ void __launch_bounds__(256) split_halves_kernel(const float* __restrict__ u, long ldu, bf16* __restrict__ out, long ldo,
+                                                           int rows, int cols) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    const float v = u[(size_t)t * ldu + c];
+    const bf16 hi = __float2bfloat16_rn(v);
+    out[(size_t)t * ldo + c] = hi;
+    out[(size_t)(rows + t) * ldo + c] = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+__global__ void __launch_bounds__(256) gate_prep_kernel(float* __restrict__ pre, const float* __restrict__ pre_lo, long ldpre,
+                                                        const float* __restrict__ u, long ldu,
                                                         const float* __restrict__ rb, const float* __restrict__ ib,
                                                         const float* __restrict__ lam, float decay_scale, int width, int bs,
                                                         const int32_t* __restrict__ positions) {
@@ -182,7 +199,12 @@ __global__ void __launch_bounds__(256) gate_prep_kernel(float* __restrict__ pre,
     const float sp = -decay_scale * softplus_f(lam[c]);
     const float bias_r = rb[c], bias_i = ib[c];
     pdl_wait();
-    const float r = sigmoid_f(pre[pr] + bias_r), g = sigmoid_f(pre[pi] + bias_i);
+    float zr = pre[pr], zi = pre[pi];
+    if (pre_lo) {                                   // the gates' sums came as two products (split_halves)
+        zr += pre_lo[pr];
+        zi += pre_lo[pi];
+    }
+    const float r = sigmoid_f(zr + bias_r), g = sigmoid_f(zi + bias_i);
     const float log_a = sp * r;
     pre[pr] = log_a;
     pre[pi] = sqrtf(-expm1f(2.0f * log_a)) * g * u[(size_t)t * ldu + c];
@@ -551,7 +573,15 @@ BROLM_API int brolm_conv_tail(const void* x, int x_dtype, long ldx, const void* 
 
 // out [tokens, width] = state * gelu_tanh(y_raw + yb) after the recurrence moved on; state at offset 0 of a slot's row.
 // pre is overwritten (log a and the recurrence's input take the places of the gates' sums).
-BROLM_API int brolm_gated_scan(void* pre, long ldpre, const void* u, long ldu, const void* y_raw, int y_dtype, long ldy,
+BROLM_API int brolm_split_halves(const void* u, long ldu, void* out, long ldo, int rows, int cols, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return BROLM_OK;
+    if ((cols + 255) / 256 > 65535) return BROLM_ERR_TOO_LARGE;
+    return launch_pdl(split_halves_kernel, dim3(rows, (cols + 255) / 256), dim3(256), 0, stream, (const float*)u, ldu, (bf16*)out,
+                      ldo, rows, cols);
+}
+
+// pre_lo: null, or the second of two products whose sum is the gates' sums (same layout and row stride as pre).
+BROLM_API int brolm_gated_scan(void* pre, const void* pre_lo, long ldpre, const void* u, long ldu, const void* y_raw, int y_dtype, long ldy,
                                const void* yb, const void* rb, const void* ib, const void* lam, float decay_scale, int width,
                                int bs, const void* positions, const void* cu_q, const void* kv_len, const void* slots,
                                void* state, long state_stride, void* out, int out_dtype, long ldo, int batch, int tokens,
@@ -559,7 +589,8 @@ BROLM_API int brolm_gated_scan(void* pre, long ldpre, const void* u, long ldu, c
     if (batch <= 0 || tokens <= 0) return BROLM_OK;
     if (width <= 0 || bs <= 0 || width % bs) return BROLM_ERR_BAD_SIZE;
     if (batch > 65535 || (width + 255) / 256 > 65535) return BROLM_ERR_TOO_LARGE;
-    int st = launch_pdl(gate_prep_kernel, dim3(tokens, (width + 255) / 256), dim3(256), 0, stream, (float*)pre, ldpre,
+    int st = launch_pdl(gate_prep_kernel, dim3(tokens, (width + 255) / 256), dim3(256), 0, stream, (float*)pre,
+                        (const float*)pre_lo, ldpre,
                         (const float*)u, ldu, (const float*)rb, (const float*)ib, (const float*)lam, decay_scale, width, bs,
                         (const int32_t*)positions);
     if (st) return st;

@@ -600,27 +600,39 @@ def conv_tail(x: torch.Tensor, in_bias: Optional[torch.Tensor], K: int, cu_q: to
 def gated_scan(pre: torch.Tensor, u: torch.Tensor, y_raw: torch.Tensor, y_bias: Optional[torch.Tensor],
                r_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor, decay_scale: float, block: int,
                positions: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
-               out: torch.Tensor, batch: int, max_q_len: int) -> None:
+               out: torch.Tensor, batch: int, max_q_len: int, pre_lo: Optional[torch.Tensor] = None) -> None:
     """The gated diagonal recurrence over the packed tokens: per channel c of block c // block,
     r, i = sigmoid(pre[t, blk, 0 / 1, o] + bias), a = exp(-decay_scale * r * softplus(lam)),
     S <- a S + sqrt(1 - a^2) i u[t, c], out[t, c] = S * gelu_tanh(y_raw[t, c] + y_bias).  S is ``state[slot, :width]``.
-    ``pre`` is overwritten.  A sequence of more than 32 tokens is scanned as 32 runs side by side that are then joined."""
+    ``pre`` is overwritten.  A sequence of more than 32 tokens is scanned as 32 runs side by side that are then joined.
+    ``pre_lo``: the gates' sums are pre + pre_lo (two products over the halves that ``split_halves`` makes)."""
     width = u.shape[1]
     assert pre.dtype == torch.float32 and u.dtype == torch.float32 and pre.stride(1) == 1 and u.stride(1) == 1
     assert pre.shape[1] == 2 * width and y_raw.stride(1) == 1 and y_raw.shape[1] == width and out.stride(1) == 1
     assert positions.dtype == torch.int32 and positions.numel() == u.shape[0]
+    if pre_lo is not None:
+        assert pre_lo.dtype == torch.float32 and pre_lo.shape == pre.shape and pre_lo.stride() == pre.stride()
     for v in (y_bias, r_bias, i_bias, lam):
         assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == width)
-    f = _fn("recurrent", "brolm_gated_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_void_p,
+    f = _fn("recurrent", "brolm_gated_scan", [c_void_p, c_void_p, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_int, c_int,
                                               c_void_p])
-    _check(f(_ptr(pre), pre.stride(0), _ptr(u), u.stride(0), _ptr(y_raw), _code(y_raw), y_raw.stride(0), _ptr(y_bias),
+    _check(f(_ptr(pre), _ptr(pre_lo), pre.stride(0), _ptr(u), u.stride(0), _ptr(y_raw), _code(y_raw), y_raw.stride(0), _ptr(y_bias),
              _ptr(r_bias), _ptr(i_bias), _ptr(lam), decay_scale, width, block, _ptr(positions),
              *_seq(cu_q, kv_len, slots, state), _ptr(out), _code(out), out.stride(0), batch, u.shape[0], max_q_len,
              _stream()), "gated_scan")
     global _launches
     _launches += 1                      # two kernels
+
+
+def split_halves(u: torch.Tensor, out: torch.Tensor) -> None:
+    """out (2 rows, cols) bfloat16 = [bf16(u); bf16(u - bf16(u))] for float32 u (rows, cols): 16 bits of u in two halves."""
+    rows, cols = u.shape
+    assert u.dtype == torch.float32 and out.dtype == torch.bfloat16 and u.stride(1) == 1 and out.stride(1) == 1
+    assert tuple(out.shape) == (2 * rows, cols)
+    f = _fn("recurrent", "brolm_split_halves", [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_void_p])
+    _check(f(_ptr(u), u.stride(0), _ptr(out), out.stride(0), rows, cols, _stream()), "split_halves")
 
 
 def block_matvec_ok(rows: int, k: int) -> bool:
@@ -1189,4 +1201,4 @@ __all__ = ["KernelBuildError", "KernelError", "build_all", "launch_count", "devi
            "rope_kv_write", "rope_kv_write_parts", "gated_act", "softcap", "linear_f32", "skinny_gemm", "skinny_qkv_rope", "skinny_ok", "skinny_parts", "skinny_rope_tiles", "gemm_tc", "gemm_tc2", "gemm_tc2_status", "gemm_tc_ok", "gemm_tc_status", "gemm_stream", "gemm_stream_ok", "gemm_stream_parts", "stream_rows",
            "gemm_stream_status", "attention_simt", "attention_prefill_mma", "attention_prefill_tc", "attention_prefill_tc_ok", "attention_prefill_tc_split", "attention_tc_status", "attention_decode_mma",
            "decode_splits", "argmax", "sample", "cast", "bias_act", "scaled_sum", "qkv_norm_write", "gate_group_norm",
-           "experts_combine", "causal_conv", "conv_tail", "gated_scan", "ssm_scan", "block_matvec_f32", "block_matvec_ok"]
+           "experts_combine", "causal_conv", "conv_tail", "gated_scan", "ssm_scan", "block_matvec_f32", "block_matvec_ok", "split_halves"]

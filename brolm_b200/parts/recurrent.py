@@ -29,11 +29,13 @@ class GatedRecurrence(Part):
     parts; in each, r = sigmoid(Ra u + ra) and i = sigmoid(Ri u + ri) with square matrices of the part's
     size.  Per channel: a = exp(-decay_scale * r * softplus(lam)), S <- a S + sqrt(1 - a^2) (i u), and the
     result is W_o (S g).  S, the gates, the decay and the convolution are float32 in every mode; the block
-    products run over float32 rows of u.
+    products run over float32 rows of u (for a prompt of a bfloat16 step: over u in two bfloat16 halves, which
+    keep 16 bits of it, with float sums).
     """
 
     kind = "mixer"
     graph_safe = True
+    SPLIT_ROWS = 64          # from this many tokens on a bfloat16 step's gate products run on the tensor cores
 
     def __init__(self, hidden: int, width: int, blocks: int, taps: int, decay_scale: float = 8.0):
         if width % blocks:
@@ -62,6 +64,11 @@ class GatedRecurrence(Part):
         self.w_o = params["o"]
         # per block the rows [Ra; Ri], as float32: the gates' products take float32 rows of u
         self.w_gates = torch.cat([params["ra"].float(), params["ri"].float()], dim=1).contiguous()
+        # the same rows as stored, when stored in bfloat16: a prompt's gate products run on the tensor cores over u in
+        # two bfloat16 halves (16 bits of u; the products with bfloat16 matrices are exact in float)
+        self.w_gates_bf16 = None
+        if params["ra"].dtype == torch.bfloat16 and params["ri"].dtype == torch.bfloat16 and self.bs % 8 == 0:
+            self.w_gates_bf16 = torch.cat([params["ra"], params["ri"]], dim=1).contiguous()
         self.y_bias, self.x_bias = _f32(params["y_bias"]), _f32(params["x_bias"])
         self.conv, self.conv_bias = _f32(params["conv"]), _f32(params["conv_bias"])
         self.r_bias, self.i_bias = _f32(params["ra_bias"]).view(-1), _f32(params["ri_bias"]).view(-1)
@@ -83,14 +90,22 @@ class GatedRecurrence(Part):
         u = torch.empty((T, W), dtype=torch.float32, device=x.device)
         kernels.causal_conv(x_raw, self.x_bias, self.conv, self.conv_bias, "none", ctx.tok_seq, ctx.positions, *seq,
                             self.tail_off, u)
-        pre = torch.empty((T, 2 * W), dtype=torch.float32, device=x.device)
+        pre_lo = None
         if kernels.block_matvec_ok(T, self.bs):
+            pre = torch.empty((T, 2 * W), dtype=torch.float32, device=x.device)
             kernels.block_matvec_f32(u, self.bs, self.w_gates, pre, 2 * self.bs)       # a handful of tokens: a stream of the matrices
+        elif ctx.dtype == torch.bfloat16 and self.w_gates_bf16 is not None and T >= self.SPLIT_ROWS:
+            halves = torch.empty((2 * T, W), dtype=torch.bfloat16, device=x.device)
+            kernels.split_halves(u, halves)
+            both = torch.empty((2 * T, 2 * W), dtype=torch.float32, device=x.device)
+            kernels.heads_linear(halves, self.bs, self.w_gates_bf16, both, 2 * self.bs)
+            pre, pre_lo = both[:T], both[T:]
         else:
+            pre = torch.empty((T, 2 * W), dtype=torch.float32, device=x.device)
             kernels.heads_linear(u, self.bs, self.w_gates, pre, 2 * self.bs)
         out = torch.empty((T, W), dtype=ctx.dtype, device=x.device)
         kernels.gated_scan(pre, u, proj[:, :W], self.y_bias, self.r_bias, self.i_bias, self.lam, self.decay_scale,
-                           self.bs, ctx.positions, *seq, out, ctx.batch, ctx.max_q_len)
+                           self.bs, ctx.positions, *seq, out, ctx.batch, ctx.max_q_len, pre_lo=pre_lo)
         kernels.conv_tail(x_raw, self.x_bias, self.taps, *seq, self.tail_off, ctx.batch)
         return linear(out, self.w_o, out_dtype=torch.float32, parts_ok=True)
 

@@ -221,6 +221,29 @@ def test_gated_scan_remembers_for_thousands_of_tokens():
     assert float(ref[-1].abs().max()) > 0.1 * float(ref[1].abs().max())
 
 
+def test_two_halves_keep_sixteen_bits_and_two_part_gate_sums_add_up():
+    g = torch.Generator().manual_seed(3)
+    u = torch.randn(37, 50, generator=g) * torch.logspace(-6, 3, 50)
+    out = torch.empty(74, 50, dtype=torch.bfloat16, device=DEV)
+    kernels.split_halves(u.to(DEV), out)
+    back = out[:37].double().cpu() + out[37:].double().cpu()
+    assert float(((back - u.double()).abs() / u.double().abs().clamp_min(1e-30)).max()) <= 2.0 ** -16
+    assert torch.equal(out[:37].cpu(), u.to(torch.bfloat16))
+    # the recurrence from sums given in two parts is the recurrence from their sum
+    W, T = 32, 100
+    pre, u2, y_raw = torch.randn(T, 2 * W, generator=g), torch.randn(T, W, generator=g), torch.randn(T, W, generator=g)
+    part = torch.randn(T, 2 * W, generator=g)
+    vecs = [torch.randn(W, generator=g).to(DEV) for _ in range(4)]
+    outs = []
+    for a, b in ((pre, None), (pre - part, part)):
+        state = torch.zeros(2, W, device=DEV)
+        o = torch.empty(T, W, device=DEV)
+        kernels.gated_scan(a.to(DEV), u2.to(DEV), y_raw.to(DEV), *vecs, 8.0, 8, i32(list(range(T))), i32([0, T]), i32([T]), i32([0]),
+                           state, o, 1, T, pre_lo=b.to(DEV) if b is not None else None)
+        outs.append(o)
+    assert rel(outs[1], outs[0].cpu()) <= 1e-5
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,P,N,groups,norm_groups,taps", [(4, 8, 16, 2, 1, 2), (2, 24, 12, 1, 3, 5), (5, 8, 40, 5, 5, 3),
                                                                 (1, 32, 64, 1, 2, 4), (2, 16, 100, 2, 4, 4), (2, 8, 128, 1, 1, 1),
